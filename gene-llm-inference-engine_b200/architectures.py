@@ -4,8 +4,11 @@ Adding an architecture means: a typed configuration class with ``from_json``, ``
 ``model_spec`` (its config.json keys translated into parts), a weight plan (its tensor names mapped
 onto the parameters of those parts), and one ``register_architecture`` call like the one below.
 """
-from .config import Architecture, LlamaConfig, register_architecture
-from .weights.plan import llama_weight_plan
+from .config import Architecture, LlamaConfig, NipadraConfig, register_architecture
+from .weights.plan import llama_weight_plan, nipadra_weight_plan
 
 register_architecture(Architecture(
     name="LlamaForCausalLM", model_types=("llama",), config_class=LlamaConfig, weight_plan=llama_weight_plan))
+
+register_architecture(Architecture(
+    name="Nipadra", model_types=("nipadra",), config_class=NipadraConfig, weight_plan=nipadra_weight_plan))

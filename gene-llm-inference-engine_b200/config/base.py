@@ -30,17 +30,20 @@ class LayerSpec:
     """The parts of one layer. ``block`` names the arrangement (see parts/block.py); ``extra`` holds
     further parts that an arrangement may name beyond the usual four (norms after the mixer or the
     feed-forward of a sandwich arrangement, a second feed-forward run in parallel, ...): the block
-    builds them by their key, with the weights under ``layers.<i>.<key>.``."""
+    builds them by their key, with the weights under ``layers.<i>.<key>.``. ``feed_forward`` (and its
+    norm) may be None for arrangements whose layers can lack one; ``block_params`` are the arrangement's
+    own constants (the residual's factor of an arrangement that normalises after the sum)."""
     mixer: PartSpec
-    feed_forward: PartSpec
+    feed_forward: Optional[PartSpec]
     mixer_norm: PartSpec
-    feed_forward_norm: PartSpec
+    feed_forward_norm: Optional[PartSpec]
     block: str = "pre_norm"
     extra: Dict[str, PartSpec] = field(default_factory=dict)
+    block_params: Dict[str, Any] = field(default_factory=dict)
 
     def __hash__(self):
         return hash((self.mixer, self.feed_forward, self.mixer_norm, self.feed_forward_norm, self.block,
-                     tuple(sorted((k, hash(v)) for k, v in self.extra.items()))))
+                     tuple(sorted((k, hash(v)) for k, v in self.extra.items())), repr(sorted(self.block_params.items()))))
 
 
 @dataclass(frozen=True)
@@ -65,6 +68,9 @@ class ModelSpec:
     tie_word_embeddings: bool
     embedding_scale: float = 1.0   # multiplier on embedding rows (1 = none)
     logit_transform: Optional[PartSpec] = None   # applied to the logits after the head (a scale, a soft cap); None = none
+    # a design without a context length of its own: ``max_position`` is then only the engine's default, and the
+    # caller's limit may exceed it
+    open_ended: bool = False
 
     def validate(self) -> None:
         n = len(self.layers)

@@ -1,7 +1,7 @@
 """One registry from an architecture's name to what builds it.
 
-``config.json``'s ``architectures[0]`` selects the entry; when that key is absent the entry whose
-``model_types`` holds ``model_type`` is taken. An entry gives the typed configuration class (with
+``config.json``'s ``architectures[0]`` (or a single name under ``architecture``) selects the entry;
+when both keys are absent the entry whose ``model_types`` holds ``model_type`` is taken. An entry gives the typed configuration class (with
 ``from_json``, ``to_json`` and ``model_spec``) and the weight plan (weights/plan.py) that maps tensor
 names of the checkpoint onto the parameters of the parts.
 """
@@ -36,6 +36,8 @@ def resolve_architecture(config_json: Dict[str, Any]) -> Architecture:
     if not isinstance(config_json, dict):
         raise ConfigError("config.json is not a JSON object")
     names = config_json.get("architectures")
+    if names is None and isinstance(config_json.get("architecture"), str):
+        names = [config_json["architecture"]]
     if isinstance(names, list) and names:
         name = names[0]
         if name in _ARCHITECTURES:

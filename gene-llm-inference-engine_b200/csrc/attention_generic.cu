@@ -9,6 +9,10 @@
 // a running max and sum, and the four warps are merged in warp order. A row's result depends only
 // on that row's query and cache contents, never on the rest of the batch.
 //
+// Options: ``sink`` adds one to the softmax's denominator (a key of score 0 without a value:
+// p_j = exp(s_j) / (1 + sum exp(s_j))); ``gate`` multiplies head h's output by sigmoid(gate[t, h]);
+// ``out_scale`` multiplies the output by a constant.
+//
 // This kernel is the whole attention of the 32-bit path and the fallback of the bfloat16 path.
 #include "common.cuh"
 
@@ -58,7 +62,8 @@ paged_attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_
                                const T* __restrict__ v_cache, T* __restrict__ out,
                                const int* __restrict__ row_req, const int* __restrict__ positions,
                                const int* __restrict__ block_tables, int table_stride, int H, int Hkv, int hd,
-                               int page_size, float scale, int window) {
+                               int page_size, float scale, int window, int sink,
+                               const float* __restrict__ gate, int gate_ld, int gate_off, float out_scale) {
     pdl_prologue();
     __shared__ float s_q[kMaxHeadDim];
     __shared__ float s_acc[kAttWarps][kMaxHeadDim];
@@ -122,21 +127,26 @@ paged_attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_
     }
     __syncthreads();
 
-    float M = -INFINITY;
+    // a sink is one more key whose score is 0 and which has no value: it enters the maximum and the sum only
+    float M = sink ? 0.f : -INFINITY;
 #pragma unroll
     for (int w = 0; w < kAttWarps; ++w) M = fmaxf(M, s_m[w]);
-    float L = 0.f;
+    float L = sink ? expf(-M) : 0.f;
     float f[kAttWarps];
 #pragma unroll
     for (int w = 0; w < kAttWarps; ++w) {
         f[w] = (s_m[w] == -INFINITY) ? 0.f : expf(s_m[w] - M);
         L += s_l[w] * f[w];
     }
+    // an output gate per head: sigmoid of a 32-bit number of the token's row of ``gate``
+    float mul = out_scale;
+    if (gate) mul *= 1.0f / (1.0f + expf(-gate[static_cast<size_t>(t) * gate_ld + gate_off + h]));
     for (int d = threadIdx.x; d < hd; d += blockDim.x) {
         float o = 0.f;
 #pragma unroll
         for (int w = 0; w < kAttWarps; ++w) o += s_acc[w][d] * f[w];
-        out[(static_cast<size_t>(t) * H + h) * hd + d] = from_float<T>(o / L);
+        o /= L;
+        out[(static_cast<size_t>(t) * H + h) * hd + d] = from_float<T>(gate || out_scale != 1.0f ? o * mul : o);
     }
 }
 
@@ -150,7 +160,8 @@ extern "C" int gi_attention_generic_supported(int hd) { return hd % 16 == 0 && h
 static int gi_attention_generic_impl(const void* q, const void* k_cache, const void* v_cache, void* out, int dtype,
                                     const int* row_req, const int* positions, const int* block_tables,
                                     int table_stride, int T, int H, int Hkv, int hd, int page_size, float scale,
-                                    int window, void* stream) {
+                                    int window, int sink, const float* gate, int gate_ld, int gate_off, float out_scale,
+                                    void* stream) {
     if (T == 0) return 0;
     GI_REQUIRE(T > 0 && H > 0 && Hkv > 0 && page_size > 0, "attention: sizes must be positive");
     GI_REQUIRE(H % Hkv == 0, "attention: %d query heads are not a multiple of %d key/value heads", H, Hkv);
@@ -163,12 +174,12 @@ static int gi_attention_generic_impl(const void* q, const void* k_cache, const v
         launch_kernel((paged_attention_generic_kernel<float>), dim3(grid), dim3(kAttWarps * 32), 0, st, 
             static_cast<const float*>(q), static_cast<const float*>(k_cache), static_cast<const float*>(v_cache),
             static_cast<float*>(out), row_req, positions, block_tables, table_stride, H, Hkv, hd, page_size, scale,
-            window);
+            window, sink, gate, gate_ld, gate_off, out_scale);
     } else if (dtype == kBF16) {
         launch_kernel((paged_attention_generic_kernel<__nv_bfloat16>), dim3(grid), dim3(kAttWarps * 32), 0, st, 
             static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k_cache),
             static_cast<const __nv_bfloat16*>(v_cache), static_cast<__nv_bfloat16*>(out), row_req, positions,
-            block_tables, table_stride, H, Hkv, hd, page_size, scale, window);
+            block_tables, table_stride, H, Hkv, hd, page_size, scale, window, sink, gate, gate_ld, gate_off, out_scale);
     } else {
         GI_REQUIRE(false, "attention: unsupported dtype code %d", dtype);
     }
@@ -177,6 +188,6 @@ static int gi_attention_generic_impl(const void* q, const void* k_cache, const v
 
 // The exported names: each runs its implementation above and, while a launch program is recorded, leaves a copy of
 // its arguments in the program (common.cuh).
-extern "C" int gi_attention_generic(const void* q, const void* k_cache, const void* v_cache, void* out, int dtype, const int* row_req, const int* positions, const int* block_tables, int table_stride, int T, int H, int Hkv, int hd, int page_size, float scale, int window, void* stream) {
-    return gi::dispatch(gi_attention_generic_impl, q, k_cache, v_cache, out, dtype, row_req, positions, block_tables, table_stride, T, H, Hkv, hd, page_size, scale, window, stream);
+extern "C" int gi_attention_generic(const void* q, const void* k_cache, const void* v_cache, void* out, int dtype, const int* row_req, const int* positions, const int* block_tables, int table_stride, int T, int H, int Hkv, int hd, int page_size, float scale, int window, int sink, const float* gate, int gate_ld, int gate_off, float out_scale, void* stream) {
+    return gi::dispatch(gi_attention_generic_impl, q, k_cache, v_cache, out, dtype, row_req, positions, block_tables, table_stride, T, H, Hkv, hd, page_size, scale, window, sink, gate, gate_ld, gate_off, out_scale, stream);
 }

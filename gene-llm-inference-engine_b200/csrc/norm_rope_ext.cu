@@ -1,0 +1,232 @@
+// Kernels of layers that normalise after the residual sum, of gated feed-forwards with other activations
+// than SiLU, and of attention whose queries and keys are normalised per head before the rotation.
+//
+//   scale_cast      acc = alpha * x (32-bit) and xn = x in the compute dtype: what a sublayer of a post-norm layer
+//                   reads (xn) and what it adds its output to (acc)
+//   residual_norm   x = w * (acc / sqrt(mean(acc^2) + eps)) in 32-bit, in one pass also the next sublayer's
+//                   xn = x (compute dtype) and acc = alpha * x
+//   gated_act       out = act(gate) * up for act in {SiLU, ReLU, tanh-GELU}
+//   norm_rope_store per token and head: optional unit-RMS norm with a weight shared by all heads, rotation of the
+//                   first 2 * rot_half dimensions by angles position * freq[i] computed here in 32-bit (no table
+//                   of max_position rows), queries to q_out, keys to the token's page row; the values stored beside
+//                   them come from any column of the same input row (the keys as projected, for a design whose
+//                   values are its keys).
+//
+// All arithmetic is 32-bit; only stores round. A row's result depends on that row only.
+#include "common.cuh"
+
+namespace gi {
+
+__device__ __forceinline__ float block_sum_256(float v, float* warp_part) {
+    v = warp_sum(v);
+    if ((threadIdx.x & 31) == 0) warp_part[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float total = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) total += warp_part[w];
+    __syncthreads();
+    return total;
+}
+
+template <typename TOut>
+__global__ void __launch_bounds__(256)
+scale_cast_kernel(const float* __restrict__ x, float* __restrict__ acc, TOut* __restrict__ xn, float alpha, size_t total) {
+    pdl_prologue();
+    for (size_t i = static_cast<size_t>(blockIdx.x) * 256 + threadIdx.x; i < total; i += static_cast<size_t>(gridDim.x) * 256) {
+        const float v = x[i];
+        acc[i] = alpha * v;
+        if (xn) xn[i] = from_float<TOut>(v);
+    }
+}
+
+// One block per row; the row's sum of squares is taken by a fixed strided assignment, a fixed xor tree and the
+// warps in index order (the order of the RMSNorm kernel), so a row never depends on the batch.
+template <typename TOut>
+__global__ void __launch_bounds__(256)
+residual_norm_kernel(const float* __restrict__ acc_in, const float* __restrict__ weight, float* __restrict__ x_out,
+                     float* __restrict__ acc_out, TOut* __restrict__ xn_out, int D, float eps, float alpha) {
+    pdl_prologue();
+    __shared__ float warp_part[8];
+    const size_t row = static_cast<size_t>(blockIdx.x) * D;
+    const float* a = acc_in + row;
+    float ss = 0.f;
+    for (int d = threadIdx.x; d < D; d += 256) ss = fmaf(a[d], a[d], ss);
+    const float total = block_sum_256(ss, warp_part);
+    const float scale = 1.0f / sqrtf(total / static_cast<float>(D) + eps);
+    for (int d = threadIdx.x; d < D; d += 256) {
+        const float v = weight[d] * (scale * a[d]);
+        x_out[row + d] = v;
+        if (acc_out) acc_out[row + d] = alpha * v;
+        if (xn_out) xn_out[row + d] = from_float<TOut>(v);
+    }
+}
+
+__device__ __forceinline__ float act_apply(float g, int act) {
+    if (act == 1) return fmaxf(g, 0.f);
+    if (act == 2) return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+    return g * (1.0f / (1.0f + expf(-g)));
+}
+
+template <typename TOut>
+__global__ void __launch_bounds__(256)
+gated_act_kernel(const float* __restrict__ gu, TOut* __restrict__ out, int I, size_t total, int act) {
+    pdl_prologue();
+    const size_t i = static_cast<size_t>(blockIdx.x) * 256 + threadIdx.x;
+    if (i >= total) return;
+    const size_t t = i / I;
+    const int c = static_cast<int>(i % I);
+    out[i] = from_float<TOut>(act_apply(gu[t * 2 * I + c], act) * gu[t * 2 * I + I + c]);
+}
+
+constexpr int kNrsWarps = 4;
+constexpr int kNrsMaxHead = 256;
+
+// One block per token, a warp per head (query heads first, then key heads).
+template <typename T>
+__global__ void __launch_bounds__(kNrsWarps * 32)
+norm_rope_store_kernel(const float* __restrict__ in, int ld, int q_off, int k_off, int v_off,
+                       const float* __restrict__ q_norm, const float* __restrict__ k_norm, float eps,
+                       const float* __restrict__ freq, int rot_half, int interleaved,
+                       const int* __restrict__ positions, const int* __restrict__ row_req,
+                       const int* __restrict__ block_tables, int table_stride,
+                       T* __restrict__ q_out, T* __restrict__ k_cache, T* __restrict__ v_cache,
+                       int H, int Hkv, int hd, int page_size, int write_kv) {
+    pdl_prologue();
+    __shared__ float s_head[kNrsWarps][kNrsMaxHead];
+    const int t = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int pos = positions[t];
+    const float* row = in + static_cast<size_t>(t) * ld;
+    size_t kv_base = 0;
+    if (write_kv) {
+        const int page = block_tables[static_cast<size_t>(row_req[t]) * table_stride + pos / page_size];
+        kv_base = (static_cast<size_t>(page) * Hkv * page_size + (pos % page_size)) * hd;
+    }
+    const int n_heads = H + (write_kv ? Hkv : 0);
+    float* sh = s_head[warp];
+    for (int head = warp; head < n_heads; head += kNrsWarps) {
+        const bool is_q = head < H;
+        const float* src = row + (is_q ? q_off + head * hd : k_off + (head - H) * hd);
+        const float* nw = is_q ? q_norm : k_norm;
+        float ss = 0.f;
+        for (int d = lane; d < hd; d += 32) {
+            const float v = src[d];
+            sh[d] = v;
+            ss = fmaf(v, v, ss);
+        }
+        ss = warp_sum(ss);
+        __syncwarp();
+        if (nw) {
+            const float scale = 1.0f / sqrtf(ss / static_cast<float>(hd) + eps);
+            for (int d = lane; d < hd; d += 32) sh[d] = nw[d] * (scale * sh[d]);
+            __syncwarp();
+        }
+        T* dst = is_q ? q_out + (static_cast<size_t>(t) * H + head) * hd
+                      : k_cache + kv_base + static_cast<size_t>(head - H) * page_size * hd;
+        const int half = freq ? rot_half : 0;
+        for (int i = lane; i < half; i += 32) {
+            const int ia = interleaved ? 2 * i : i, ib = interleaved ? 2 * i + 1 : i + half;
+            float sn, cs;
+            sincosf(static_cast<float>(pos) * freq[i], &sn, &cs);
+            const float a = sh[ia], b = sh[ib];
+            dst[ia] = from_float<T>(a * cs - b * sn);
+            dst[ib] = from_float<T>(b * cs + a * sn);
+        }
+        for (int d = 2 * half + lane; d < hd; d += 32) dst[d] = from_float<T>(sh[d]);
+        if (!is_q) {
+            const float* vsrc = row + v_off + (head - H) * hd;
+            T* vdst = v_cache + kv_base + static_cast<size_t>(head - H) * page_size * hd;
+            for (int d = lane; d < hd; d += 32) vdst[d] = from_float<T>(vsrc[d]);
+        }
+        __syncwarp();
+    }
+}
+
+}  // namespace gi
+
+using namespace gi;
+
+static int gi_scale_cast_impl(const float* x, float* acc, void* xn, int xn_dtype, float alpha, long long total, void* stream) {
+    if (total == 0) return 0;
+    GI_REQUIRE(total > 0, "scale_cast: the size must be positive");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const unsigned blocks = static_cast<unsigned>(std::min<long long>((total + 255) / 256, 148 * 16));
+    if (xn_dtype == kBF16)
+        launch_kernel((scale_cast_kernel<__nv_bfloat16>), dim3(blocks), dim3(256), 0, st, x, acc, static_cast<__nv_bfloat16*>(xn), alpha, static_cast<size_t>(total));
+    else
+        launch_kernel((scale_cast_kernel<float>), dim3(blocks), dim3(256), 0, st, x, acc, static_cast<float*>(xn), alpha, static_cast<size_t>(total));
+    return check_launch("scale_cast");
+}
+
+static int gi_residual_norm_impl(const float* acc_in, const float* weight, float* x_out, float* acc_out, void* xn_out,
+                                 int xn_dtype, int rows, int D, float eps, float alpha, void* stream) {
+    if (rows == 0) return 0;
+    GI_REQUIRE(rows > 0 && D > 0, "residual_norm: sizes must be positive (rows=%d, D=%d)", rows, D);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (xn_dtype == kBF16)
+        launch_kernel((residual_norm_kernel<__nv_bfloat16>), dim3(rows), dim3(256), 0, st, acc_in, weight, x_out, acc_out,
+                      static_cast<__nv_bfloat16*>(xn_out), D, eps, alpha);
+    else
+        launch_kernel((residual_norm_kernel<float>), dim3(rows), dim3(256), 0, st, acc_in, weight, x_out, acc_out,
+                      static_cast<float*>(xn_out), D, eps, alpha);
+    return check_launch("residual_norm");
+}
+
+static int gi_gated_act_impl(const float* gate_up, void* out, int out_dtype, int T, int I, int act, void* stream) {
+    if (T == 0) return 0;
+    GI_REQUIRE(T > 0 && I > 0, "gated_act: sizes must be positive (T=%d, I=%d)", T, I);
+    GI_REQUIRE(act >= 0 && act <= 2, "gated_act: unknown activation code %d", act);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const size_t total = static_cast<size_t>(T) * I;
+    const unsigned blocks = static_cast<unsigned>((total + 255) / 256);
+    if (out_dtype == kBF16)
+        launch_kernel((gated_act_kernel<__nv_bfloat16>), dim3(blocks), dim3(256), 0, st, gate_up, static_cast<__nv_bfloat16*>(out), I, total, act);
+    else if (out_dtype == kF32)
+        launch_kernel((gated_act_kernel<float>), dim3(blocks), dim3(256), 0, st, gate_up, static_cast<float*>(out), I, total, act);
+    else
+        GI_REQUIRE(false, "gated_act: unsupported output dtype code %d", out_dtype);
+    return check_launch("gated_act");
+}
+
+static int gi_norm_rope_store_impl(const float* in, int ld, int q_off, int k_off, int v_off, const float* q_norm,
+                                   const float* k_norm, float eps, const float* freq, int rot_half, int interleaved,
+                                   const int* positions, const int* row_req, const int* block_tables, int table_stride,
+                                   void* q_out, void* k_cache, void* v_cache, int dtype, int T, int H, int Hkv, int hd,
+                                   int page_size, int write_kv, void* stream) {
+    if (T == 0) return 0;
+    GI_REQUIRE(T > 0 && H > 0 && Hkv > 0 && hd > 0 && page_size > 0, "norm_rope_store: sizes must be positive");
+    GI_REQUIRE(hd <= kNrsMaxHead, "norm_rope_store: head size %d exceeds %d", hd, kNrsMaxHead);
+    GI_REQUIRE(2 * rot_half <= hd, "norm_rope_store: rotary size %d exceeds the head size %d", 2 * rot_half, hd);
+    GI_REQUIRE(q_off >= 0 && k_off >= 0 && v_off >= 0 && q_off + H * hd <= ld && k_off + Hkv * hd <= ld && v_off + Hkv * hd <= ld,
+               "norm_rope_store: the columns of queries, keys or values lie outside the input row of %d", ld);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (dtype == kF32)
+        launch_kernel((norm_rope_store_kernel<float>), dim3(T), dim3(kNrsWarps * 32), 0, st, in, ld, q_off, k_off, v_off, q_norm,
+                      k_norm, eps, freq, rot_half, interleaved, positions, row_req, block_tables, table_stride,
+                      static_cast<float*>(q_out), static_cast<float*>(k_cache), static_cast<float*>(v_cache), H, Hkv, hd,
+                      page_size, write_kv);
+    else if (dtype == kBF16)
+        launch_kernel((norm_rope_store_kernel<__nv_bfloat16>), dim3(T), dim3(kNrsWarps * 32), 0, st, in, ld, q_off, k_off, v_off,
+                      q_norm, k_norm, eps, freq, rot_half, interleaved, positions, row_req, block_tables, table_stride,
+                      static_cast<__nv_bfloat16*>(q_out), static_cast<__nv_bfloat16*>(k_cache),
+                      static_cast<__nv_bfloat16*>(v_cache), H, Hkv, hd, page_size, write_kv);
+    else
+        GI_REQUIRE(false, "norm_rope_store: unsupported dtype code %d", dtype);
+    return check_launch("norm_rope_store");
+}
+
+extern "C" int gi_scale_cast(const float* x, float* acc, void* xn, int xn_dtype, float alpha, long long total, void* stream) {
+    return gi::dispatch(gi_scale_cast_impl, x, acc, xn, xn_dtype, alpha, total, stream);
+}
+
+extern "C" int gi_residual_norm(const float* acc_in, const float* weight, float* x_out, float* acc_out, void* xn_out, int xn_dtype, int rows, int D, float eps, float alpha, void* stream) {
+    return gi::dispatch(gi_residual_norm_impl, acc_in, weight, x_out, acc_out, xn_out, xn_dtype, rows, D, eps, alpha, stream);
+}
+
+extern "C" int gi_gated_act(const float* gate_up, void* out, int out_dtype, int T, int I, int act, void* stream) {
+    return gi::dispatch(gi_gated_act_impl, gate_up, out, out_dtype, T, I, act, stream);
+}
+
+extern "C" int gi_norm_rope_store(const float* in, int ld, int q_off, int k_off, int v_off, const float* q_norm, const float* k_norm, float eps, const float* freq, int rot_half, int interleaved, const int* positions, const int* row_req, const int* block_tables, int table_stride, void* q_out, void* k_cache, void* v_cache, int dtype, int T, int H, int Hkv, int hd, int page_size, int write_kv, void* stream) {
+    return gi::dispatch(gi_norm_rope_store_impl, in, ld, q_off, k_off, v_off, q_norm, k_norm, eps, freq, rot_half, interleaved, positions, row_req, block_tables, table_stride, q_out, k_cache, v_cache, dtype, T, H, Hkv, hd, page_size, write_kv, stream);
+}

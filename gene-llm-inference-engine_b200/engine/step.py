@@ -67,6 +67,7 @@ class StepContext:
         self.seg_len = views["seg_len"]
         self._tables = views["tables"]
         self._cache: Dict = {}
+        self.carry: Dict = {}      # what a part leaves ready for the part that runs next (cleared when a forward pass starts)
         self.all_single = all(s.length == 1 for s in segments)
         self.max_context = max((s.first_position + s.length for s in segments), default=0)
         # longest context among requests that bring a single token, rounded up to 1024 positions
@@ -225,7 +226,8 @@ class StepEngine:
         # decode-only steps are captured into CUDA graphs, one per (requests, wanted rows, context bucket)
         # (only when every part says that its launches depend on nothing but the step's shape)
         self.use_graphs = use_graphs and all(
-            getattr(layer.mixer, "graph_safe", False) and getattr(layer.feed_forward, "graph_safe", False)
+            getattr(layer.mixer, "graph_safe", False) and
+            (getattr(layer, "feed_forward", None) is None or getattr(layer.feed_forward, "graph_safe", False))
             for layer in model.layers)
         self._graphs: Dict[Tuple, Tuple] = {}
         self.graph_replays = 0

@@ -188,6 +188,150 @@ def rope_store(qkv: torch.Tensor, positions: torch.Tensor, row_req: torch.Tensor
         "rope_store")
 
 
+ACTIVATIONS = {"silu": 0, "relu": 1, "gelu_tanh": 2}
+
+
+def scale_cast(x: torch.Tensor, acc: torch.Tensor, xn: Optional[torch.Tensor], alpha: float) -> None:
+    """acc = alpha * x (32-bit) and, when given, xn = x in xn's dtype."""
+    if acc.shape != x.shape or (xn is not None and xn.shape != x.shape):
+        raise KernelError("scale_cast: shapes do not agree")
+    check(lib().gi_scale_cast(_dev(x, "x", torch.float32), _dev(acc, "acc", torch.float32), 0 if xn is None else _dev(xn, "xn"),
+                              F32 if xn is None else dtype_code(xn.dtype), float(alpha), x.numel(), _stream()), "scale_cast")
+
+
+def residual_norm(acc: torch.Tensor, weight: torch.Tensor, x_out: torch.Tensor, eps: float, alpha: float = 1.0,
+                  acc_out: Optional[torch.Tensor] = None, xn_out: Optional[torch.Tensor] = None) -> None:
+    """x_out = weight * (acc / sqrt(mean(acc^2) + eps)) per row, in 32-bit; optionally also acc_out = alpha * x_out
+    (it may be ``acc`` itself) and xn_out = x_out in xn_out's dtype: what the next sublayer of a layer that
+    normalises after the residual sum adds to and reads."""
+    n, D = acc.shape
+    if x_out.shape != acc.shape or weight.numel() != D:
+        raise KernelError("residual_norm: shapes of acc, weight and x_out do not agree")
+    for t, name in ((acc_out, "acc_out"), (xn_out, "xn_out")):
+        if t is not None and t.shape != acc.shape:
+            raise KernelError(f"residual_norm: {name} has the wrong shape")
+    check(lib().gi_residual_norm(_dev(acc, "acc", torch.float32), _dev(weight, "weight", torch.float32),
+                                 _dev(x_out, "x_out", torch.float32), _opt(acc_out, "acc_out", torch.float32),
+                                 0 if xn_out is None else _dev(xn_out, "xn_out"),
+                                 F32 if xn_out is None else dtype_code(xn_out.dtype), n, D, float(eps), float(alpha),
+                                 _stream()), "residual_norm")
+
+
+def gated_act(gate_up: torch.Tensor, out: torch.Tensor, activation: str) -> None:
+    """out = act(gate_up[:, :I]) * gate_up[:, I:] for act in ACTIVATIONS."""
+    T, I = out.shape
+    if gate_up.shape != (T, 2 * I):
+        raise KernelError("gated_act: gate_up must be [T, 2I] for out [T, I]")
+    if activation not in ACTIVATIONS:
+        raise KernelError(f"gated_act: unknown activation '{activation}' (known: {', '.join(sorted(ACTIVATIONS))})")
+    check(lib().gi_gated_act(_dev(gate_up, "gate_up", torch.float32), _dev(out, "out"), dtype_code(out.dtype), T, I,
+                             ACTIVATIONS[activation], _stream()), "gated_act")
+
+
+def norm_rope_store(proj: torch.Tensor, q_offset: int, k_offset: int, v_offset: int, q_norm: Optional[torch.Tensor],
+                    k_norm: Optional[torch.Tensor], eps: float, freq: Optional[torch.Tensor], interleaved: bool,
+                    positions: torch.Tensor, row_req: torch.Tensor, block_tables: torch.Tensor, q_out: torch.Tensor,
+                    k_cache: torch.Tensor, v_cache: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int,
+                    page_size: int, write_kv: bool = True) -> None:
+    """From the 32-bit projections ``proj`` [T, ld] (query heads from column q_offset, key heads from k_offset,
+    value heads from v_offset, which may be the keys' columns): per head an optional unit-RMS norm with the
+    shared weight ``q_norm`` / ``k_norm`` [hd], then the rotation of the first 2 * len(freq) dimensions by
+    position * freq[i] (angles computed on the device in 32-bit), queries to ``q_out`` [T, H*hd], keys and
+    values into the token's page row."""
+    T, ld = proj.shape
+    if q_out.shape != (T, num_heads * head_dim):
+        raise KernelError("norm_rope_store: q_out must be [T, H*hd]")
+    if k_cache.dtype != q_out.dtype or v_cache.dtype != q_out.dtype:
+        raise KernelError("norm_rope_store: q_out and the cache must have one dtype")
+    if k_cache.shape[1:] != (num_kv_heads, page_size, head_dim) or v_cache.shape != k_cache.shape:
+        raise KernelError("norm_rope_store: the cache must be [pages, Hkv, page_size, hd]")
+    for w, name in ((q_norm, "q_norm"), (k_norm, "k_norm")):
+        if w is not None and w.numel() != head_dim:
+            raise KernelError(f"norm_rope_store: {name} must have head_dim values")
+    check(lib().gi_norm_rope_store(
+        _dev(proj, "proj", torch.float32), ld, int(q_offset), int(k_offset), int(v_offset),
+        _opt(q_norm, "q_norm", torch.float32), _opt(k_norm, "k_norm", torch.float32), float(eps),
+        _opt(freq, "freq", torch.float32), 0 if freq is None else freq.numel(), int(interleaved),
+        _dev(positions, "positions", torch.int32), _dev(row_req, "row_req", torch.int32),
+        _dev(block_tables, "block_tables", torch.int32), block_tables.shape[1], _dev(q_out, "q_out"),
+        _dev(k_cache, "k_cache"), _dev(v_cache, "v_cache"), dtype_code(q_out.dtype), T, num_heads, num_kv_heads,
+        head_dim, page_size, int(write_kv), _stream()), "norm_rope_store")
+
+
+def causal_conv(proj: torch.Tensor, offset: int, weight: torch.Tensor, bias: torch.Tensor, state: torch.Tensor,
+                state_offset: int, row_req: torch.Tensor, seg_start: torch.Tensor, seg_len: torch.Tensor,
+                state_slots: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t, c] = silu(bias[c] + sum_j weight[c, j] * u(t - taps + 1 + j, c)) over the channels
+    proj[:, offset:offset + C] of each request's rows; inputs before a segment's first row come from the request's
+    state (``state`` [slots, floats per slot], the [taps-1, C] block at ``state_offset``), which afterwards
+    holds the last taps-1 inputs. Two launches."""
+    T, ld = proj.shape
+    C, taps = weight.shape
+    if out.shape != (T, C) or bias.numel() != C:
+        raise KernelError("causal_conv: shapes of weight, bias and out do not agree")
+    if state.dim() != 2 or state_offset < 0 or state_offset + (taps - 1) * C > state.shape[1]:
+        raise KernelError("causal_conv: the conv state does not fit the slot")
+    R = seg_start.numel()
+    check(lib().gi_causal_conv(_dev(proj, "proj", torch.float32), ld, int(offset), _dev(weight, "weight", torch.float32),
+                               _dev(bias, "bias", torch.float32), _dev(state, "state", torch.float32), state.shape[1],
+                               int(state_offset), _dev(row_req, "row_req", torch.int32), _dev(seg_start, "seg_start", torch.int32),
+                               _dev(seg_len, "seg_len", torch.int32), _dev(state_slots, "state_slots", torch.int32),
+                               _dev(out, "out", torch.float32), C, taps, T, R, _stream()), "causal_conv")
+    if taps > 1:
+        count_launches(1)
+
+
+def linear_scan(q: torch.Tensor, q_offset: int, k: torch.Tensor, k_offset: int, v: torch.Tensor, v_offset: int,
+                num_heads: int, group: int, dk: int, dv: int, activate: bool, state: torch.Tensor, state_offset: int,
+                seg_start: torch.Tensor, seg_len: torch.Tensor, state_slots: torch.Tensor, out: torch.Tensor,
+                decay: Optional[torch.Tensor] = None, dt: Optional[torch.Tensor] = None, dt_offset: int = 0,
+                dt_bias: Optional[torch.Tensor] = None, a_log: Optional[torch.Tensor] = None,
+                skip: Optional[torch.Tensor] = None) -> None:
+    """The recurrence S_t = a_t S_(t-1) + b_t k_t v_t^T, o_t = S_t^T q_t + skip * v_t per head over each
+    request's rows in order, the state [H, dk, dv] carried in the request's slot of ``state`` [slots, floats]
+    at ``state_offset``. q, k [T, ld] hold H / group heads of dk from their offsets (head h reads head
+    h // group), v holds H heads of dv. Either ``decay`` [H] (a constant, b = 1) or ``dt`` [T, ld] with
+    ``dt_bias`` and ``a_log`` [H] (dt' = softplus(dt + bias), a = exp(-exp(a_log) dt'), b = dt').
+    ``activate``: SiLU on q, k, v as they are read. All 32-bit."""
+    T = out.shape[0]
+    if out.shape != (T, num_heads * dv):
+        raise KernelError("linear_scan: out must be [T, H*dv]")
+    kv_heads = num_heads // group
+    for t, off, width, name in ((q, q_offset, kv_heads * dk, "q"), (k, k_offset, kv_heads * dk, "k"), (v, v_offset, num_heads * dv, "v")):
+        if t.dim() != 2 or t.shape[0] != T or off < 0 or off + width > t.shape[1]:
+            raise KernelError(f"linear_scan: {name} does not hold its heads inside a row")
+    if decay is None and (dt is None or dt_bias is None or a_log is None or dt_offset + num_heads > dt.shape[1]):
+        raise KernelError("linear_scan: give constant decays or step sizes with their bias and rates")
+    for t, name in ((decay, "decay"), (dt_bias, "dt_bias"), (a_log, "a_log"), (skip, "skip")):
+        if t is not None and t.numel() != num_heads:
+            raise KernelError(f"linear_scan: {name} must have one value per head")
+    if state.dim() != 2 or state_offset < 0 or state_offset + num_heads * dk * dv > state.shape[1]:
+        raise KernelError("linear_scan: the state does not fit the slot")
+    R = seg_start.numel()
+    check(lib().gi_linear_scan(
+        _dev(q, "q", torch.float32), q.shape[1], int(q_offset), _dev(k, "k", torch.float32), k.shape[1], int(k_offset),
+        _dev(v, "v", torch.float32), v.shape[1], int(v_offset), num_heads, group, dk, dv, int(bool(activate)),
+        _opt(decay, "decay", torch.float32), _opt(dt, "dt", torch.float32), 0 if dt is None else dt.shape[1], int(dt_offset),
+        _opt(dt_bias, "dt_bias", torch.float32), _opt(a_log, "a_log", torch.float32), _opt(skip, "skip", torch.float32),
+        _dev(state, "state", torch.float32), state.shape[1], int(state_offset), _dev(seg_start, "seg_start", torch.int32),
+        _dev(seg_len, "seg_len", torch.int32), _dev(state_slots, "state_slots", torch.int32), _dev(out, "out", torch.float32),
+        R, _stream()), "linear_scan")
+
+
+def gated_group_norm(y: torch.Tensor, gate: torch.Tensor, gate_offset: int, weight: torch.Tensor, out: torch.Tensor,
+                     groups: int, eps: float, gate_first: bool, out_scale: float = 1.0) -> None:
+    """Unit-RMS norm of y [T, W] in ``groups`` equal parts, times ``weight`` [W], with a gate from
+    gate[:, gate_offset:gate_offset + W]: ``gate_first`` norms y * silu(gate); else the normed values are multiplied
+    by sigmoid(gate). ``out_scale``: a constant factor."""
+    T, W = y.shape
+    if out.shape != (T, W) or weight.numel() != W or gate.dim() != 2 or gate.shape[0] != T:
+        raise KernelError("gated_group_norm: shapes do not agree")
+    check(lib().gi_gated_group_norm(_dev(y, "y", torch.float32), _dev(gate, "gate", torch.float32), gate.shape[1],
+                                    int(gate_offset), _dev(weight, "weight", torch.float32), _dev(out, "out"),
+                                    dtype_code(out.dtype), T, W, int(groups), float(eps), int(bool(gate_first)),
+                                    float(out_scale), _stream()), "gated_group_norm")
+
+
 def copy_pages(cache: torch.Tensor, src: torch.Tensor, dst: torch.Tensor) -> None:
     """cache is [arrays, pages, ...]; copies page src[i] to page dst[i] in every array."""
     n_arrays = cache.shape[0]
@@ -201,9 +345,14 @@ def copy_pages(cache: torch.Tensor, src: torch.Tensor, dst: torch.Tensor) -> Non
 def attention_generic(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor,
                       row_req: torch.Tensor, positions: torch.Tensor, block_tables: torch.Tensor,
                       num_heads: int, num_kv_heads: int, head_dim: int, page_size: int, scale: float,
-                      window: Optional[int] = None) -> None:
-    """Causal attention of every row of ``q`` [T, H*hd] over its request's pages."""
+                      window: Optional[int] = None, sink: bool = False, gate: Optional[torch.Tensor] = None,
+                      gate_offset: int = 0, out_scale: float = 1.0) -> None:
+    """Causal attention of every row of ``q`` [T, H*hd] over its request's pages. ``sink``: one more in the
+    softmax's denominator; ``gate`` [T, ld] 32-bit: head h's output times sigmoid(gate[t, gate_offset + h]);
+    ``out_scale``: a constant factor on the output."""
     T = q.shape[0]
+    if gate is not None and (gate.dim() != 2 or gate.shape[0] != T or gate_offset < 0 or gate_offset + num_heads > gate.shape[1]):
+        raise KernelError("attention: the gate must be [T, ld] with the heads' columns inside a row")
     if q.shape != (T, num_heads * head_dim) or out.shape != q.shape or out.dtype != q.dtype:
         raise KernelError("attention: q and out must be [T, H*hd] of one dtype")
     if k_cache.dtype != q.dtype or v_cache.dtype != q.dtype:
@@ -214,7 +363,8 @@ def attention_generic(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Ten
         _dev(q, "q"), _dev(k_cache, "k_cache"), _dev(v_cache, "v_cache"), _dev(out, "out"), dtype_code(q.dtype),
         _dev(row_req, "row_req", torch.int32), _dev(positions, "positions", torch.int32),
         _dev(block_tables, "block_tables", torch.int32), block_tables.shape[1], T, num_heads, num_kv_heads,
-        head_dim, page_size, float(scale), int(window or 0), _stream()), "attention")
+        head_dim, page_size, float(scale), int(window or 0), int(bool(sink)), _opt(gate, "gate", torch.float32),
+        0 if gate is None else gate.shape[1], int(gate_offset), float(out_scale), _stream()), "attention")
 
 
 def attention_supported(head_dim: int) -> bool:

@@ -26,7 +26,21 @@ _SIGNATURES = {
                       c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "gi_copy_pages": [c_void_p, c_longlong, c_int, c_longlong, c_void_p, c_void_p, c_int, c_void_p],
     "gi_attention_generic": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
-                             c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
+                             c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_int, c_int, c_float,
+                             c_void_p],
+    "gi_scale_cast": [c_void_p, c_void_p, c_void_p, c_int, c_float, c_longlong, c_void_p],
+    "gi_residual_norm": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_float, c_void_p],
+    "gi_gated_act": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    "gi_norm_rope_store": [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int,
+                           c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                           c_int, c_int, c_int, c_void_p],
+    "gi_causal_conv": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_longlong, c_longlong, c_void_p, c_void_p,
+                       c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    "gi_linear_scan": [c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                       c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_longlong,
+                       c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
+    "gi_gated_group_norm": [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float,
+                            c_int, c_float, c_void_p],
     "gi_gemm_simt": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                      c_int, c_void_p],
     "gi_gemm_tc": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong,

@@ -18,7 +18,16 @@ class AttentionMixer:
 
     Params: ``hidden_size``, ``num_heads``, ``num_kv_heads``, ``head_dim``, ``scale`` (multiplied
     after the dot product), ``window`` (None = all keys) and ``position`` (a PartSpec).
-    Weights: ``w_qkv`` [(H+2Hkv)*hd, hidden] and ``w_o`` [hidden, H*hd]."""
+    Weights: ``w_qkv`` [(H+2Hkv)*hd, hidden] and ``w_o`` [hidden, H*hd].
+
+    Options (each absent by default; any of them takes the mixer off the fused [q; k; v] product with
+    rotation in its epilogue and onto the 32-bit projection followed by the norm+rotation+store kernel):
+    ``values`` = "keys": there is no value projection; the keys as projected, before norm and rotation, are
+    stored as the values (``w_qkv`` then has no value rows). ``qk_norm_eps``: queries and keys are
+    normalised per head to unit RMS and multiplied by ``q_norm`` / ``k_norm`` [hd] (shared by the heads)
+    before the rotation. ``sink``: the softmax's denominator has one more term, exp(0). ``head_gate``:
+    ``w_qkv`` ends with H more rows, and head h's output is multiplied by the sigmoid of its row's product
+    with the input. ``out_scale``: a constant on the mixer's output (applied before the output projection)."""
 
     graph_safe = True      # launches depend only on the step's shape: decode steps may be captured in a CUDA graph
 
@@ -37,7 +46,27 @@ class AttentionMixer:
                              f"(multiples of 16 up to 256)")
         pos_spec = params.get("position") or PartSpec("none", {})
         self.position = build_part(POSITION_ENCODINGS, "position encoding", pos_spec, {}, build)
-        qkv_rows = (self.num_heads + 2 * self.num_kv_heads) * self.head_dim
+        self.values_are_keys = params.get("values", "projected") == "keys"
+        if params.get("values", "projected") not in ("projected", "keys"):
+            raise ValueError(f"attention: unknown source of values '{params.get('values')}'")
+        self.qk_norm_eps = params.get("qk_norm_eps")
+        self.sink = bool(params.get("sink", False))
+        self.head_gate = bool(params.get("head_gate", False))
+        self.out_scale = float(params.get("out_scale", 1.0))
+        on_device = getattr(self.position, "freq", None) is not None
+        self.extended = (self.values_are_keys or self.qk_norm_eps is not None or self.sink or self.head_gate
+                         or self.out_scale != 1.0 or on_device)
+        if self.extended and getattr(self.position, "cos", None) is not None:
+            raise ValueError("attention: with these options the rotation's angles are computed on the device "
+                             "(position encoding 'rope_on_device' or 'none')")
+        self.q_norm = self.k_norm = None
+        if self.qk_norm_eps is not None:
+            for name in ("q_norm", "k_norm"):
+                if tuple(weights[name].shape) != (self.head_dim,):
+                    raise ValueError(f"attention: {name} has shape {tuple(weights[name].shape)}, expected ({self.head_dim},)")
+                setattr(self, name, weights[name].to(device=build.device, dtype=torch.float32).contiguous())
+        qkv_rows = (self.num_heads + (1 if self.values_are_keys else 2) * self.num_kv_heads) * self.head_dim + \
+            (self.num_heads if self.head_gate else 0)
         if tuple(weights["w_qkv"].shape) != (qkv_rows, self.hidden_size):
             raise ValueError(f"attention: w_qkv has shape {tuple(weights['w_qkv'].shape)}, expected "
                              f"({qkv_rows}, {self.hidden_size})")
@@ -47,7 +76,7 @@ class AttentionMixer:
         self.w_o = Linear(weights["w_o"], build.compute_dtype, build.device, tiles=build.weight_tiles)
         self.dtype = build.compute_dtype
         # bfloat16 with a head size the tensor-core kernels are built for; else the general kernel
-        self.fast = self.dtype is torch.bfloat16 and kernels.attention_fast_supported(
+        self.fast = self.dtype is torch.bfloat16 and not self.extended and kernels.attention_fast_supported(
             self.head_dim, self.num_heads, self.num_kv_heads)
         self._prefill_rows = {}
         if self.fast:
@@ -97,6 +126,9 @@ class AttentionMixer:
         k_cache, v_cache = ctx.pages(run.cache_layer)
         tables = ctx.block_tables(run.cache_layer)
         q = ctx.scratch("q", (T, H * hd), self.dtype)
+        if self.extended:
+            self._forward_extended(ctx, run, xn, x, q, k_cache, v_cache, tables, then)
+            return
         if self.dtype is torch.bfloat16 and kernels.gemm_rope_store_supported(
                 T, self.hidden_size, H, Hkv, hd, self.position.cos, self.position.interleaved):
             # rotation and page store in the epilogue of the product
@@ -128,4 +160,24 @@ class AttentionMixer:
         else:
             kernels.attention_generic(q, k_cache, v_cache, att, ctx.row_req, ctx.positions, tables, H, Hkv, hd,
                                       ctx.page_size, self.scale, self.window)
+        self.w_o.forward(att, x, accumulate=True, then=then)
+
+    def _forward_extended(self, ctx, run, xn, x, q, k_cache, v_cache, tables, then) -> None:
+        """The mixer with options: projections to 32-bit, then per head norm, rotation and page store, the
+        general attention kernel with sink and gate, and the output projection."""
+        T = xn.shape[0]
+        H, Hkv, hd = self.num_heads, self.num_kv_heads, self.head_dim
+        proj = ctx.scratch("att_proj", (T, self.w_qkv.out_features), torch.float32)
+        self.w_qkv.forward(xn, proj)
+        k_off = H * hd
+        v_off = k_off if self.values_are_keys else k_off + Hkv * hd
+        gate_off = v_off + Hkv * hd
+        kernels.norm_rope_store(proj, 0, k_off, v_off, self.q_norm, self.k_norm, self.qk_norm_eps or 0.0,
+                                getattr(self.position, "freq", None), self.position.interleaved, ctx.positions,
+                                ctx.row_req, tables, q, k_cache, v_cache, H, Hkv, hd, ctx.page_size,
+                                write_kv=run.writes_cache)
+        att = ctx.scratch("att", (T, H * hd), self.dtype)
+        kernels.attention_generic(q, k_cache, v_cache, att, ctx.row_req, ctx.positions, tables, H, Hkv, hd,
+                                  ctx.page_size, self.scale, self.window, sink=self.sink,
+                                  gate=proj if self.head_gate else None, gate_offset=gate_off, out_scale=self.out_scale)
         self.w_o.forward(att, x, accumulate=True, then=then)

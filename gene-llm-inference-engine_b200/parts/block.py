@@ -51,6 +51,66 @@ class PreNormBlock:
         self.feed_forward.forward(ctx, xn, x)
 
 
+@register_block("post_norm")
+class PostNormBlock:
+    """x <- N1(alpha x + mixer(x)) and, when the layer has a feed-forward, x <- N2(alpha x + ff(x)): the norm
+    comes after the residual sum and the sublayers read the stream x itself. ``block_params``: ``alpha`` (1).
+
+    The stream stays 32-bit. A sublayer reads ``xn`` (x in the compute dtype; x itself on the 32-bit path)
+    and adds its output to ``acc``, which holds alpha x. One kernel takes the norm of acc into x and, in the
+    same pass, prepares xn and acc of the sublayer that follows; the next layer of this arrangement finds them
+    ready (``ctx.carry``), so that a layer costs one memory-bound kernel per sublayer besides the sublayers."""
+
+    def __init__(self, layer_spec, weights, build):
+        self.alpha = float(layer_spec.block_params.get("alpha", 1.0))
+        self.mixer_norm = build_part(NORMS, "norm", layer_spec.mixer_norm, sub_weights(weights, "mixer_norm."), build)
+        self.mixer = build_part(MIXERS, "mixer", layer_spec.mixer, sub_weights(weights, "mixer."), build)
+        self.feed_forward = self.feed_forward_norm = None
+        if layer_spec.feed_forward is not None:
+            self.feed_forward_norm = build_part(NORMS, "norm", layer_spec.feed_forward_norm,
+                                                sub_weights(weights, "feed_forward_norm."), build)
+            self.feed_forward = build_part(FEED_FORWARDS, "feed-forward", layer_spec.feed_forward,
+                                           sub_weights(weights, "feed_forward."), build)
+        self.dtype = build.compute_dtype
+
+    def forward(self, ctx, run, x: torch.Tensor) -> None:
+        from ..ops import kernels
+        T = x.shape[0]
+        acc = ctx.scratch("post_norm_acc", tuple(x.shape), torch.float32)
+        xn = x if self.dtype is torch.float32 else ctx.scratch("normed", tuple(x.shape), self.dtype)
+        carry = getattr(ctx, "carry", None)
+        ready = carry is not None and carry.get("post_norm") == (x.data_ptr(), self.alpha)
+        key = _launch_key(ctx, (self.mixer_norm, None), (self.mixer, run))
+        second = self.feed_forward is not None
+
+        def mixer_half():
+            if not ready:
+                kernels.scale_cast(x, acc, None if xn is x else xn, self.alpha)
+            self.mixer.forward(ctx, run, xn, acc)
+            # with a feed-forward to come, the same pass prepares what it reads and adds to
+            kernels.residual_norm(acc, self.mixer_norm.weight, x, self.mixer_norm.eps, self.alpha,
+                                  acc_out=acc, xn_out=None if xn is x else xn)
+
+        if key is not None:
+            ctx.recorded(self, ("mixer", run, T, ready) + key, mixer_half)
+        else:
+            mixer_half()
+        ctx.tap("attn_out", run.layer, x)
+        if second:
+            def feed_forward_half():
+                self.feed_forward.forward(ctx, xn, acc)
+                kernels.residual_norm(acc, self.feed_forward_norm.weight, x, self.feed_forward_norm.eps, self.alpha,
+                                      acc_out=acc, xn_out=None if xn is x else xn)
+            key = _launch_key(ctx, (self.feed_forward_norm, None), (self.feed_forward, None))
+            if key is not None:
+                ctx.recorded(self, ("feed_forward", T) + key, feed_forward_half)
+            else:
+                feed_forward_half()
+        ctx.tap("ffn_out", run.layer, x)
+        if carry is not None:
+            carry["post_norm"] = (x.data_ptr(), self.alpha)      # acc = alpha x and xn = x hold for whoever runs next
+
+
 def build_extra(layer_spec, key: str, table, what: str, weights, build):
     """Builds the part that a layer's ``extra`` names ``key`` (for arrangements with more parts than
     the usual four), with the weights under ``<key>.``."""

@@ -9,11 +9,12 @@ from .registry import register_feed_forward
 
 
 @register_feed_forward("swiglu")
+@register_feed_forward("gated_mlp")
 class SwiGLUFeedForward:
-    """x += W_down (silu(W_gate xn) * (W_up xn)) (src/model/transformer.cpp:437-450).
+    """x += W_down (act(W_gate xn) * (W_up xn)) (src/model/transformer.cpp:437-450).
 
-    Params: ``hidden_size``, ``intermediate_size``. Weights: ``w_gate_up`` [2I, hidden] (gate rows
-    first, then up rows) and ``w_down`` [hidden, I]."""
+    Params: ``hidden_size``, ``intermediate_size`` and optionally ``activation`` ("silu", the default; "relu";
+    "gelu_tanh"). Weights: ``w_gate_up`` [2I, hidden] (gate rows first, then up rows) and ``w_down`` [hidden, I]."""
 
     graph_safe = True      # launches depend only on the step's shape: decode steps may be captured in a CUDA graph
 
@@ -21,6 +22,9 @@ class SwiGLUFeedForward:
     def __init__(self, params, weights, build):
         self.hidden_size = int(params["hidden_size"])
         self.intermediate_size = int(params["intermediate_size"])
+        self.activation = params.get("activation", "silu")
+        if self.activation not in kernels.ACTIVATIONS:
+            raise ValueError(f"gated feed-forward: unknown activation '{self.activation}'")
         I, D = self.intermediate_size, self.hidden_size
         if tuple(weights["w_gate_up"].shape) != (2 * I, D):
             raise ValueError(f"swiglu: w_gate_up has shape {tuple(weights['w_gate_up'].shape)}, expected ({2 * I}, {D})")
@@ -42,10 +46,14 @@ class SwiGLUFeedForward:
     def forward(self, ctx, xn: torch.Tensor, x: torch.Tensor) -> None:
         T = xn.shape[0]
         h = ctx.scratch("ffn_hidden", (T, self.intermediate_size), self.dtype)
-        if self.dtype is torch.bfloat16 and kernels.gemm_swiglu_supported(T, self.intermediate_size, self.hidden_size):
+        if self.activation == "silu" and self.dtype is torch.bfloat16 and \
+                kernels.gemm_swiglu_supported(T, self.intermediate_size, self.hidden_size):
             kernels.gemm_swiglu(xn, self.w_gate_up.weight, h)      # activation in the product's epilogue
         else:
             gu = ctx.scratch("gate_up", (T, 2 * self.intermediate_size), torch.float32)
             self.w_gate_up.forward(xn, gu)
-            kernels.swiglu(gu, h)
+            if self.activation == "silu":
+                kernels.swiglu(gu, h)
+            else:
+                kernels.gated_act(gu, h, self.activation)
         self.w_down.forward(h, x, accumulate=True)

@@ -35,7 +35,10 @@ class DecoderModel:
         self.device = device
         self.hidden_size = spec.hidden_size
         self.vocab_size = spec.vocab_size
-        self.max_position = min(spec.max_position, max_position) if max_position else spec.max_position
+        if spec.open_ended:      # the design bounds no position: the caller's limit stands, the spec's is the default
+            self.max_position = int(max_position) if max_position else spec.max_position
+        else:
+            self.max_position = min(spec.max_position, max_position) if max_position else spec.max_position
         build = BuildContext(device=device, compute_dtype=compute_dtype, max_position=self.max_position,
                              weight_tiles=weight_tiles)
 
@@ -117,6 +120,8 @@ class DecoderModel:
         """Runs the tokens of ``ctx`` through every scheduled layer and returns 32-bit logits
         [wanted rows, vocab] (None when no row wants logits)."""
         T = ctx.n_tokens
+        if hasattr(ctx, "carry"):
+            ctx.carry.clear()
         x = ctx.scratch("residual", (T, self.hidden_size), torch.float32)
         with ctx.range("embedding"):
             kernels.embed(self.embedding, ctx.tokens, x, self.embedding_scale, ctx.feedback)

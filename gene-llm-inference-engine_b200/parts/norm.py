@@ -13,7 +13,9 @@ from .registry import register_norm
 class RMSNorm:
     """out = weight * (x / sqrt(mean(x^2) + eps)), computed in 32-bit from the 32-bit residual
     stream (src/kernels/kernels.cpp:72-83); the weight is used as is (no ``1 + w``) and is kept in
-    32-bit whatever the checkpoint stores. Params: ``size``, ``eps``. Weights: ``weight`` [size]."""
+    32-bit whatever the checkpoint stores. Params: ``size``, ``eps`` and optionally ``weight_offset`` (0): a
+    checkpoint that stores its norm weights around zero and applies ``offset + w`` is served by adding the
+    offset once, in 32-bit, when the model is built. Weights: ``weight`` [size]."""
 
     def __init__(self, params, weights, build):
         self.size = int(params["size"])
@@ -21,7 +23,10 @@ class RMSNorm:
         w = weights["weight"]
         if tuple(w.shape) != (self.size,):
             raise ValueError(f"rmsnorm: weight has shape {tuple(w.shape)}, expected ({self.size},)")
+        self.weight_offset = float(params.get("weight_offset", 0.0))
         self.weight = w.to(device=build.device, dtype=torch.float32).contiguous()
+        if self.weight_offset:
+            self.weight += self.weight_offset
 
     def launch_key(self, ctx):
         """Its one launch depends on the number of rows only (which the caller's key holds)."""

@@ -71,3 +71,30 @@ class NoPosition:
 
     def __init__(self, params, weights, build):
         pass
+
+
+@register_position_encoding("rope_on_device")
+class RotaryOnDevice:
+    """Rotary position encoding whose angles are computed where they are applied: the kernel multiplies
+    the 32-bit position by the pair's 32-bit frequency and takes sine and cosine, so no table of
+    ``max_position`` rows exists and no position is too far. Params: ``head_dim``, ``theta``, ``pairing``
+    ("interleaved" or "half_split"), optional ``rotary_dim`` (< head_dim rotates only the first dims).
+    ``freq`` [rotary_dim / 2] = theta^(-2i / rotary_dim), taken in double and rounded once."""
+
+    applies = "qk_before_store"
+    cos = None
+    sin = None
+    not_weights = ("freq",)
+
+    def __init__(self, params, weights, build):
+        self.head_dim = int(params["head_dim"])
+        self.rotary_dim = int(params.get("rotary_dim") or self.head_dim)
+        if self.rotary_dim % 2 or self.rotary_dim > self.head_dim:
+            raise ValueError(f"rope: rotary_dim {self.rotary_dim} must be even and at most head_dim {self.head_dim}")
+        pairing = params.get("pairing", "half_split")
+        if pairing not in ("half_split", "interleaved"):
+            raise ValueError(f"rope: unknown pairing '{pairing}'")
+        self.interleaved = pairing == "interleaved"
+        i = np.arange(self.rotary_dim // 2, dtype=np.float64)
+        freq = np.power(float(params["theta"]), -2.0 * i / self.rotary_dim)
+        self.freq = torch.from_numpy(freq.astype(np.float32)).to(build.device).contiguous()

@@ -1,0 +1,215 @@
+"""Mixers that keep a state of fixed size per request instead of keys and values.
+
+Both run the same recurrence kernel, S_t = a_t S_(t-1) + b_t k_t v_t^T and o_t = S_t^T q_t (+ skip v_t), per
+head over each request's rows in order, with the 32-bit state [H, dk, dv] in the request's state slot
+(``ctx.state(layer)[slot]``; the engine hands a new request a zeroed slot). They differ in where q, k, v, a and
+b come from and in the gated norm that follows.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..cache import StateNeed
+from ..ops import kernels
+from ..ops.linear import Linear
+from .registry import register_mixer
+
+
+def _vector(weights, name: str, n: int, build, what: str) -> torch.Tensor:
+    w = weights[name]
+    if w.numel() != n or w.dim() != 1:
+        raise ValueError(f"{what}: {name} has shape {tuple(w.shape)}, expected ({n},)")
+    return w.to(device=build.device, dtype=torch.float32).contiguous()
+
+
+@register_mixer("linear_attention")
+class LinearAttentionMixer:
+    """Linear attention with a constant decay per head: q, k [H, dk] and v [H, dv] are activated
+    projections of the input, S_t = decay_h S_(t-1) + k_t v_t^T, o_t = S_t^T q_t with no other scale; the
+    heads together are normalised to unit RMS (weight ``norm`` [H*dv]), multiplied by sigmoid(W_g input) and
+    projected by ``w_o``.
+
+    Params: ``hidden_size``, ``num_heads``, ``key_dim``, ``value_dim``, ``decay`` (one per head), ``norm_eps``,
+    ``activation`` ("silu" or "none") and optionally ``out_scale``. Weights: ``w_in`` [(2 H dk + 2 H dv), hidden]
+    (rows of q, k, v, then the gate), ``w_o`` [hidden, H dv], ``norm`` [H dv]."""
+
+    graph_safe = True
+
+    def __init__(self, params, weights, build):
+        self.hidden_size = int(params["hidden_size"])
+        self.num_heads, self.dk, self.dv = int(params["num_heads"]), int(params["key_dim"]), int(params["value_dim"])
+        self.eps = float(params["norm_eps"])
+        self.activate = params.get("activation", "silu") == "silu"
+        if params.get("activation", "silu") not in ("silu", "none"):
+            raise ValueError(f"linear attention: unknown activation '{params.get('activation')}'")
+        self.out_scale = float(params.get("out_scale", 1.0))
+        decay = [float(d) for d in params["decay"]]
+        if len(decay) != self.num_heads:
+            raise ValueError("linear attention: one decay per head is needed")
+        if self.dk > 256:
+            raise ValueError(f"linear attention: key size {self.dk} exceeds what the recurrence kernel holds (256)")
+        H, dk, dv, D = self.num_heads, self.dk, self.dv, self.hidden_size
+        self.decay = torch.tensor(decay, dtype=torch.float32, device=build.device)
+        rows = 2 * H * dk + 2 * H * dv
+        if tuple(weights["w_in"].shape) != (rows, D):
+            raise ValueError(f"linear attention: w_in has shape {tuple(weights['w_in'].shape)}, expected ({rows}, {D})")
+        if tuple(weights["w_o"].shape) != (D, H * dv):
+            raise ValueError(f"linear attention: w_o has shape {tuple(weights['w_o'].shape)}, expected ({D}, {H * dv})")
+        self.w_in = Linear(weights["w_in"], build.compute_dtype, build.device, tiles=build.weight_tiles)
+        self.w_o = Linear(weights["w_o"], build.compute_dtype, build.device, tiles=build.weight_tiles)
+        self.norm = _vector(weights, "norm", H * dv, build, "linear attention")
+        self.dtype = build.compute_dtype
+
+    def cache_need(self):
+        return None
+
+    def state_need(self):
+        return StateNeed((self.num_heads * self.dk * self.dv,), "float32")
+
+    def launch_key(self, ctx, run):
+        return (run.cache_layer, ctx.n_requests)
+
+    takes_then = True
+
+    def forward(self, ctx, run, xn: torch.Tensor, x: torch.Tensor, then=None) -> None:
+        T = xn.shape[0]
+        H, dk, dv = self.num_heads, self.dk, self.dv
+        proj = ctx.scratch("lin_att_proj", (T, self.w_in.out_features), torch.float32)
+        self.w_in.forward(xn, proj)
+        o = ctx.scratch("lin_att_out", (T, H * dv), torch.float32)
+        kernels.linear_scan(proj, 0, proj, H * dk, proj, 2 * H * dk, H, 1, dk, dv, self.activate,
+                            ctx.state(run.cache_layer), 0, ctx.seg_start, ctx.seg_len, ctx.state_slots, o, decay=self.decay)
+        y = ctx.scratch("lin_att_normed", (T, H * dv), self.dtype)
+        kernels.gated_group_norm(o, proj, 2 * H * dk + H * dv, self.norm, y, 1, self.eps, gate_first=False,
+                                 out_scale=self.out_scale)
+        self.w_o.forward(y, x, accumulate=True, then=then)
+
+
+@register_mixer("state_space")
+class StateSpaceMixer:
+    """A selective state-space mixer in its scalar-decay (state-space duality) form. With inner = H P:
+    ``w_in`` maps the input to [z: inner | x: inner | B: G N | C: G N | dt: H]; x, B and C pass a causal
+    convolution per channel (``conv`` [channels, taps], the last column the current token's, bias
+    ``conv_bias``, zeros before the start) and SiLU; dt <- softplus(dt + ``dt_bias``) without a clamp; per head
+    (head h reads group h // (H / G)): S_t = exp(-exp(``a_log``_h) dt) S_(t-1) + dt B_t x_t^T (S is N x P),
+    y_t = S_t^T C_t + ``skip``_h x_t; then y * silu(z), unit RMS in ``norm_groups`` equal parts, times ``norm``,
+    and the projection ``w_o``. The request's state slot holds S and, behind it, the last taps-1 inputs of the
+    convolution [taps-1, channels].
+
+    Params: ``hidden_size``, ``num_heads``, ``head_dim`` (P), ``state_size`` (N), ``groups``, ``conv_taps``,
+    ``norm_groups``, ``norm_eps`` and optionally ``out_scale``."""
+
+    graph_safe = True
+
+    def __init__(self, params, weights, build):
+        self.hidden_size = int(params["hidden_size"])
+        self.num_heads, self.head_dim = int(params["num_heads"]), int(params["head_dim"])
+        self.state_size, self.groups = int(params["state_size"]), int(params["groups"])
+        self.taps, self.norm_groups = int(params["conv_taps"]), int(params["norm_groups"])
+        self.eps = float(params["norm_eps"])
+        self.out_scale = float(params.get("out_scale", 1.0))
+        H, P, N, G, D = self.num_heads, self.head_dim, self.state_size, self.groups, self.hidden_size
+        if H % G:
+            raise ValueError("state space: heads must be a multiple of groups")
+        if N > 256:
+            raise ValueError(f"state space: state size {N} exceeds what the recurrence kernel holds (256)")
+        if not (1 <= self.taps <= 17):
+            raise ValueError(f"state space: {self.taps} convolution taps are not supported (1 to 17)")
+        self.inner = H * P
+        self.channels = self.inner + 2 * G * N
+        if self.inner % self.norm_groups:
+            raise ValueError("state space: heads * head_dim must split into norm_groups equal parts")
+        rows = 2 * self.inner + 2 * G * N + H
+        if tuple(weights["w_in"].shape) != (rows, D):
+            raise ValueError(f"state space: w_in has shape {tuple(weights['w_in'].shape)}, expected ({rows}, {D})")
+        if tuple(weights["w_o"].shape) != (D, self.inner):
+            raise ValueError(f"state space: w_o has shape {tuple(weights['w_o'].shape)}, expected ({D}, {self.inner})")
+        if tuple(weights["conv"].shape) != (self.channels, self.taps):
+            raise ValueError(f"state space: conv has shape {tuple(weights['conv'].shape)}, expected ({self.channels}, {self.taps})")
+        self.w_in = Linear(weights["w_in"], build.compute_dtype, build.device, tiles=build.weight_tiles)
+        self.w_o = Linear(weights["w_o"], build.compute_dtype, build.device, tiles=build.weight_tiles)
+        self.conv = weights["conv"].to(device=build.device, dtype=torch.float32).contiguous()
+        self.conv_bias = _vector(weights, "conv_bias", self.channels, build, "state space")
+        self.dt_bias = _vector(weights, "dt_bias", H, build, "state space")
+        self.a_log = _vector(weights, "a_log", H, build, "state space")
+        self.skip = _vector(weights, "skip", H, build, "state space")
+        self.norm = _vector(weights, "norm", self.inner, build, "state space")
+        self.dtype = build.compute_dtype
+
+    def cache_need(self):
+        return None
+
+    def state_need(self):
+        return StateNeed((self.num_heads * self.state_size * self.head_dim + (self.taps - 1) * self.channels,), "float32")
+
+    def launch_key(self, ctx, run):
+        return (run.cache_layer, ctx.n_requests)
+
+    takes_then = True
+
+    def forward(self, ctx, run, xn: torch.Tensor, x: torch.Tensor, then=None) -> None:
+        T = xn.shape[0]
+        H, P, N, G = self.num_heads, self.head_dim, self.state_size, self.groups
+        inner, C = self.inner, self.channels
+        state = ctx.state(run.cache_layer)
+        proj = ctx.scratch("ssm_proj", (T, self.w_in.out_features), torch.float32)
+        self.w_in.forward(xn, proj)
+        xbc = ctx.scratch("ssm_conv", (T, C), torch.float32)
+        kernels.causal_conv(proj, inner, self.conv, self.conv_bias, state, H * N * P, ctx.row_req, ctx.seg_start,
+                            ctx.seg_len, ctx.state_slots, xbc)
+        y = ctx.scratch("ssm_out", (T, inner), torch.float32)
+        # q = C, k = B, v = x; a and b from the step size
+        kernels.linear_scan(xbc, inner + G * N, xbc, inner, xbc, 0, H, H // G, N, P, False, state, 0, ctx.seg_start,
+                            ctx.seg_len, ctx.state_slots, y, dt=proj, dt_offset=inner + C, dt_bias=self.dt_bias,
+                            a_log=self.a_log, skip=self.skip)
+        yn = ctx.scratch("ssm_normed", (T, inner), self.dtype)
+        kernels.gated_group_norm(y, proj, 0, self.norm, yn, self.norm_groups, self.eps, gate_first=True,
+                                 out_scale=self.out_scale)
+        self.w_o.forward(yn, x, accumulate=True, then=then)
+
+
+@register_mixer("parallel")
+class ParallelMixer:
+    """Several mixers side by side on the same input: x += sum_i scale_i * mixer_i(xn). Params: ``branches``,
+    a list of (name, PartSpec, scale); branch ``name`` is built from the weights under ``<name>.`` with its
+    scale as ``out_scale``. At most one branch may keep pages and at most one may keep state."""
+
+    def __init__(self, params, weights, build):
+        from ..config import PartSpec
+        from .registry import MIXERS, build_part, sub_weights
+        self.branches = []
+        for name, spec, scale in params["branches"]:
+            spec = PartSpec(spec.kind, dict(spec.params, out_scale=float(scale)))
+            self.branches.append((name, build_part(MIXERS, "mixer", spec, sub_weights(weights, name + "."), build)))
+        if sum(m.cache_need() is not None for _, m in self.branches) > 1 or \
+                sum(m.state_need() is not None for _, m in self.branches) > 1:
+            raise ValueError("parallel mixer: at most one branch may keep pages and at most one may keep state")
+        for name, m in self.branches:
+            setattr(self, name, m)
+        self.graph_safe = all(getattr(m, "graph_safe", False) for _, m in self.branches)
+
+    def cache_need(self):
+        return next((m.cache_need() for _, m in self.branches if m.cache_need() is not None), None)
+
+    def state_need(self):
+        return next((m.state_need() for _, m in self.branches if m.state_need() is not None), None)
+
+    def launch_key(self, ctx, run):
+        key = ()
+        for _, m in self.branches:
+            fn = getattr(m, "launch_key", None)
+            k = fn(ctx, run) if fn is not None else None
+            if k is None:
+                return None
+            key += tuple(k)
+        return key
+
+    takes_then = True
+
+    def forward(self, ctx, run, xn: torch.Tensor, x: torch.Tensor, then=None) -> None:
+        for i, (_, m) in enumerate(self.branches):
+            last = i == len(self.branches) - 1
+            if last and then is not None and getattr(m, "takes_then", False):
+                m.forward(ctx, run, xn, x, then=then)
+            else:
+                m.forward(ctx, run, xn, x)

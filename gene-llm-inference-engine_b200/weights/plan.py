@@ -8,7 +8,7 @@ from __future__ import annotations
 
 import fnmatch
 from dataclasses import dataclass, field
-from typing import Callable, Dict, List, Tuple
+from typing import Callable, Dict, List, Optional, Tuple
 
 import torch
 
@@ -18,6 +18,9 @@ class TensorRule:
     name: str
     shape: Tuple[int, ...]
     kind: str = "matrix"     # "matrix", "vector" (norm weights and the like) or "table" (integers)
+    # how random weights are drawn for this tensor, when not as its kind says: (mean, std) of a normal
+    # distribution, or ("uniform", low, high)
+    init: Optional[Tuple] = None
 
 
 @dataclass
@@ -75,6 +78,70 @@ def llama_weight_plan(cfg) -> WeightPlan:
         return out
 
     return WeightPlan(rules, ignorable, assemble)
+
+
+def nipadra_weight_plan(cfg) -> WeightPlan:
+    """Tensor names and shapes of a Nipadra checkpoint: ``embed``, ``final.norm`` and, for layer i,
+    ``l<i>.norm1`` / ``l<i>.norm2``, the mixer's tensors under ``l<i>.mix.`` and the feed-forward's under
+    ``l<i>.mlp.``. Projections that read the same input are concatenated row-wise into one matrix product
+    each: [q; k; v; g] of a lightning mixer, [q; k; g] of the windowed attention, [gate; up] of the feed-forward."""
+    D, V = cfg.width, cfg.vocab
+    zero = (0.0, 0.05)                   # norm weights of this design are stored around zero
+    rules = [TensorRule("embed", (V, D))]
+    for i, layer in enumerate(cfg.layers):
+        p = f"l{i}."
+        rules.append(TensorRule(p + "norm1", (D,), "vector", zero))
+        if layer.ff is not None:
+            rules.append(TensorRule(p + "norm2", (D,), "vector", zero))
+        m = layer.mixer
+        if layer.type == "lightning":
+            rules += [TensorRule(p + "mix.q", (m.heads * m.dim, D)), TensorRule(p + "mix.k", (m.heads * m.dim, D)),
+                      TensorRule(p + "mix.v", (m.heads * m.vdim, D)), TensorRule(p + "mix.g", (m.heads * m.vdim, D)),
+                      TensorRule(p + "mix.o", (D, m.heads * m.vdim)), TensorRule(p + "mix.norm", (m.heads * m.vdim,), "vector")]
+        else:
+            a, s = m.left, m.right
+            q = p + "mix.left."
+            rules += [TensorRule(q + "q", (a.heads * a.dim, D)), TensorRule(q + "k", (a.kv_heads * a.dim, D)),
+                      TensorRule(q + "q.norm", (a.dim,), "vector"), TensorRule(q + "k.norm", (a.dim,), "vector"),
+                      TensorRule(q + "g", (a.heads, D)), TensorRule(q + "o", (D, a.heads * a.vdim))]
+            q = p + "mix.right."
+            rules += [TensorRule(q + "in", (2 * s.inner + 2 * s.groups * s.state + s.heads, D)),
+                      TensorRule(q + "conv", (s.conv_channels, s.conv), "vector", (0.0, 0.4)),
+                      TensorRule(q + "conv.b", (s.conv_channels,), "vector", (0.0, 0.1)),
+                      TensorRule(q + "dt_bias", (s.heads,), "vector", ("uniform", -3.0, 0.5)),
+                      TensorRule(q + "A_log", (s.heads,), "vector", ("uniform", -1.5, 1.0)),
+                      TensorRule(q + "D", (s.heads,), "vector", (1.0, 0.2)),
+                      TensorRule(q + "norm", (s.inner,), "vector"), TensorRule(q + "o", (D, s.inner))]
+        if layer.ff is not None:
+            rules += [TensorRule(p + "mlp.gate", (layer.ff, D)), TensorRule(p + "mlp.up", (layer.ff, D)),
+                      TensorRule(p + "mlp.down", (D, layer.ff))]
+    rules.append(TensorRule("final.norm", (D,), "vector", zero))
+
+    def assemble(t: Dict[str, torch.Tensor]) -> Dict[str, torch.Tensor]:
+        out: Dict[str, torch.Tensor] = {"embedding.weight": t["embed"], "head.weight": t["embed"],
+                                        "final_norm.weight": t["final.norm"]}
+        for i, layer in enumerate(cfg.layers):
+            p, q = f"l{i}.", f"layers.{i}."
+            out[q + "mixer_norm.weight"] = t[p + "norm1"]
+            if layer.type == "lightning":
+                out[q + "mixer.w_in"] = _cat([t[p + "mix.q"], t[p + "mix.k"], t[p + "mix.v"], t[p + "mix.g"]])
+                out[q + "mixer.w_o"] = t[p + "mix.o"]
+                out[q + "mixer.norm"] = t[p + "mix.norm"]
+            else:
+                a, b = p + "mix.left.", q + "mixer.left."
+                out[b + "w_qkv"] = _cat([t[a + "q"], t[a + "k"], t[a + "g"]])
+                out[b + "q_norm"], out[b + "k_norm"], out[b + "w_o"] = t[a + "q.norm"], t[a + "k.norm"], t[a + "o"]
+                a, b = p + "mix.right.", q + "mixer.right."
+                out[b + "w_in"], out[b + "w_o"], out[b + "norm"] = t[a + "in"], t[a + "o"], t[a + "norm"]
+                out[b + "conv"], out[b + "conv_bias"] = t[a + "conv"], t[a + "conv.b"]
+                out[b + "dt_bias"], out[b + "a_log"], out[b + "skip"] = t[a + "dt_bias"], t[a + "A_log"], t[a + "D"]
+            if layer.ff is not None:
+                out[q + "feed_forward_norm.weight"] = t[p + "norm2"]
+                out[q + "feed_forward.w_gate_up"] = _cat([t[p + "mlp.gate"], t[p + "mlp.up"]])
+                out[q + "feed_forward.w_down"] = t[p + "mlp.down"]
+        return out
+
+    return WeightPlan(rules, [], assemble)
 
 
 def _cat(parts: List[torch.Tensor]) -> torch.Tensor:

@@ -4,7 +4,8 @@ configuration and a seed.
 Every tensor has its own generator seeded from (seed, tensor name), so the values do not depend on
 the order in which tensors are drawn or on the dtype they are stored in: values are drawn in
 32-bit and rounded to bfloat16 (nearest even) only when stored so. Matrices are N(0, std); norm
-weights are ``norm_mean + N(0, norm_std)``.
+weights are ``norm_mean + N(0, norm_std)``; a tensor whose rule carries ``init`` (a mean and a deviation,
+or a uniform range) is drawn as that says.
 """
 from __future__ import annotations
 
@@ -44,8 +45,14 @@ def write_random_model(config_json: Dict[str, Any], seed: int, out_dir: str, dty
             if rule.kind == "table":
                 yield rule.name, torch.zeros(rule.shape, dtype=torch.int32)
                 continue
+            init = getattr(rule, "init", None)
+            if init is not None and init[0] == "uniform":
+                yield rule.name, torch.rand(rule.shape, generator=g, dtype=torch.float32).mul_(init[2] - init[1]).add_(init[1]).to(store)
+                continue
             t = torch.randn(rule.shape, generator=g, dtype=torch.float32)
-            if rule.kind == "vector":
+            if init is not None:
+                t = t.mul_(init[1]).add_(init[0])
+            elif rule.kind == "vector":
                 t = t.mul_(norm_std).add_(norm_mean)
             else:
                 t = t.mul_(std)
