@@ -5,6 +5,7 @@
     python bench.py --scenario mixed|prefix [--shape ...] [--dtype bfloat16|float32]
                                         (continuous batching / shared prefixes through the scheduler, see run_scenario)
     python bench.py --scenario sizes [--shape ...]   (decode steps at a grid of batch sizes and contexts, see run_sizes)
+    python bench.py --scenario nipadra               (the Nipadra design beside Llama at equal layer sizes, see run_nipadra)
 
 Prints ONE JSON line. ``value`` is decoded tokens per second at batch 8 and context 8192, timed on
 the device over exactly K decode steps (one step = one token for every request of the batch);
@@ -385,6 +386,190 @@ def run_sizes(args):
     return 0
 
 
+# ---------------------------------------------------------------------------------------------- Nipadra beside Llama
+def nipadra_config(width, ff, layers, vocab, heads, head_dim, kv_heads, window):
+    """A Nipadra model with the layer sizes of a Llama shape: every layer has the same feed-forward, three of four
+    mixers are lightning attention (heads of 128), every fourth is the windowed attention beside the state-space mixer."""
+    lh = width // 128
+    decay = [1.0 - 2.0 ** (-5 - 3 * i / max(1, lh - 1)) for i in range(lh)]
+    light = {"type": "lightning", "mixer": {"heads": lh, "dim": 128, "vdim": 128, "decay": decay}, "mlp": {"ff": ff, "kind": "dense"}}
+    par = {"type": "parallel", "mixer": {
+        "left": {"heads": heads, "kv_heads": kv_heads, "dim": head_dim, "vdim": head_dim, "mask": {"size": window},
+                 "rot": {"base": 500000.0, "dims": head_dim}, "scale": head_dim ** -0.5},
+        "right": {"heads": width // 64, "vdim": 64, "state": 128, "groups": 1, "conv": 4, "norm_groups": 1},
+        "left_scale": 0.5, "right_scale": 0.5}, "mlp": {"ff": ff, "kind": "dense"}}
+    return {"architecture": "Nipadra", "width": width, "vocab": vocab, "norm": {"eps": 1e-6}, "postln_alpha": 2.0,
+            "layers": [par if i % 4 == 2 else light for i in range(layers)]}
+
+
+def time_calls(fn, iters=8, flush=None):
+    """Median device time of ``fn()`` in ms (CUDA events), the L2 cache swept between calls."""
+    import torch
+    for _ in range(3):
+        fn()
+    times = []
+    for _ in range(iters):
+        if flush is not None:
+            flush.zero_()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        times.append(a.elapsed_time(b))
+    return sorted(times)[len(times) // 2]
+
+
+def nipadra_kernel_table(width, heads, kv_heads, head_dim, window, T, pk):
+    """Each kernel of the new design alone, and the like kernel of the Llama path, at the sizes of one layer:
+    a prompt portion of ``T`` tokens of one request and a decode step of 8 requests. ``frac`` is the time the
+    kernel's algorithmic bytes (or, where larger, its multiply-adds on the tensor cores) need at the measured peaks,
+    divided by the time it took."""
+    import torch
+    from geneinfer_b200.ops import kernels as K
+    dev = torch.device("cuda:0")
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    rows = []
+
+    def add(name, like, fn, nbytes, flops=0.0):
+        ms = time_calls(fn, flush=flush)
+        ideal = max(nbytes / (pk["hbm_gbs"] * 1e9), flops / (pk["bf16_tflops"] * 1e12)) * 1e3
+        rows.append({"kernel": name, "like": like, "us": round(ms * 1e3, 1), "frac": round(ideal / ms, 3)})
+
+    def seg(R, n):
+        i32 = dict(dtype=torch.int32, device=dev)
+        return (torch.arange(R, **i32) * n, torch.full((R,), n, **i32), torch.arange(R, **i32),
+                torch.arange(R, **i32).repeat_interleave(n))
+
+    D = width
+    for what, R, n in (("prefill", 1, T), ("decode", 8, 1)):
+        rows_n = R * n
+        x = torch.randn(rows_n, D, device=dev)
+        acc, xo = torch.empty_like(x), torch.empty_like(x)
+        xn = torch.empty(rows_n, D, dtype=torch.bfloat16, device=dev)
+        w = torch.ones(D, device=dev)
+        add(f"residual_norm ({what})", "rmsnorm", lambda: K.residual_norm(x, w, xo, 1e-6, 2.0, acc_out=acc, xn_out=xn), rows_n * D * 14)
+        add(f"rmsnorm, Llama ({what})", "", lambda: K.rmsnorm(x, w, xn, 1e-6), rows_n * D * 6)
+        # lightning attention: heads of 128 x 128
+        H = D // 128
+        proj = torch.randn(rows_n, 4 * D, device=dev) * 0.5
+        out = torch.empty(rows_n, D, device=dev)
+        state = torch.zeros(R, H * 128 * 128, device=dev)
+        s0, sl, slots, rr = seg(R, n)
+        decay = torch.full((H,), 0.99, device=dev)
+        scan_bytes = rows_n * D * 4 * 4 + 2 * R * H * 128 * 128 * 4
+        add(f"linear_scan, constant decay ({what})", "attention", lambda: K.linear_scan(
+            proj, 0, proj, D, proj, 2 * D, H, 1, 128, 128, True, state, 0, s0, sl, slots, out, decay=decay), scan_bytes)
+        y = torch.empty(rows_n, D, dtype=torch.bfloat16, device=dev)
+        add(f"gated_group_norm ({what})", "swiglu", lambda: K.gated_group_norm(out, proj, 3 * D, w, y, 1, 1e-6, False), rows_n * D * 10)
+        # state space: heads of 64, state 128
+        Hs, N = D // 64, 128
+        C = D + 2 * N
+        proj2 = torch.randn(rows_n, 2 * D + 2 * N + Hs, device=dev) * 0.5
+        conv_w, conv_b = torch.randn(C, 4, device=dev) * 0.3, torch.zeros(C, device=dev)
+        st2 = torch.zeros(R, Hs * N * 64 + 3 * C, device=dev)
+        xbc = torch.empty(rows_n, C, device=dev)
+        add(f"causal_conv ({what})", "rope_store", lambda: K.causal_conv(proj2, D, conv_w, conv_b, st2, Hs * N * 64, rr, s0, sl, slots, xbc),
+            rows_n * C * 8)
+        dtb, alog, skip = torch.zeros(Hs, device=dev), torch.zeros(Hs, device=dev), torch.ones(Hs, device=dev)
+        add(f"linear_scan, step sizes ({what})", "attention", lambda: K.linear_scan(
+            xbc, D + N, xbc, D, xbc, 0, Hs, Hs, N, 64, False, st2, 0, s0, sl, slots, out, dt=proj2, dt_offset=D + C, dt_bias=dtb,
+            a_log=alog, skip=skip), rows_n * (D * 8 + 2 * N * 4) + 2 * R * Hs * N * 64 * 4)
+        # windowed attention: norm + rotation + store, then attention over a context of T
+        page = 16
+        ctx_len = T
+        n_pages = R * ((ctx_len + page - 1) // page)
+        kc = torch.randn(n_pages, kv_heads, page, head_dim, device=dev).to(torch.bfloat16)
+        vc = torch.randn(n_pages, kv_heads, page, head_dim, device=dev).to(torch.bfloat16)
+        tables = torch.arange(n_pages, dtype=torch.int32, device=dev).view(R, -1)
+        pos = (torch.arange(n, dtype=torch.int32, device=dev) + (ctx_len - n)).repeat(R)
+        qkw = (heads + kv_heads) * head_dim
+        proj3 = torch.randn(rows_n, qkw + heads, device=dev)
+        q = torch.empty(rows_n, heads * head_dim, dtype=torch.bfloat16, device=dev)
+        nw = torch.ones(head_dim, device=dev)
+        freq = torch.rand(head_dim // 2, device=dev)
+        add(f"norm_rope_store ({what})", "rope_store", lambda: K.norm_rope_store(
+            proj3, 0, heads * head_dim, heads * head_dim, nw, nw, 1e-6, freq, True, pos, rr, tables, q, kc, vc, heads, kv_heads,
+            head_dim, page), rows_n * (qkw * 4 + (heads + 2 * kv_heads) * head_dim * 2))
+        qkv = torch.randn(rows_n, (heads + 2 * kv_heads) * head_dim, device=dev)
+        cs = torch.rand(ctx_len, head_dim // 2, device=dev)
+        add(f"rope_store, Llama ({what})", "", lambda: K.rope_store(qkv, pos, rr, tables, cs, cs, False, q, kc, vc, heads, kv_heads,
+                                                                   head_dim, page), rows_n * (heads + 2 * kv_heads) * head_dim * 6)
+        att = torch.empty_like(q)
+        keys_seen = sum(min(window, p + 1) for p in range(ctx_len - n, ctx_len))
+        att_flops = 4.0 * R * keys_seen * heads * head_dim
+        att_bytes = R * min(ctx_len, window + n) * kv_heads * head_dim * 4 + rows_n * heads * head_dim * 4
+        rows_dec = torch.arange(R, dtype=torch.int32, device=dev)
+        per_tile = 128 // (heads // kv_heads)
+        work = torch.tensor([(t, min(per_tile, n - t), 0) for t in range(0, n, per_tile)][::-1], dtype=torch.int32, device=dev)
+        chunk = K.attention_chunk_keys()
+        n_chunks = (ctx_len + chunk - 1) // chunk
+        part_o = torch.empty(R, heads * n_chunks * head_dim, device=dev)
+        part_ml = torch.empty(R, heads * n_chunks * 2, device=dev)
+
+        def attend(win, **ep):
+            if n == 1:
+                K.attention_decode(q, kc, vc, att, rows_dec, rr, pos, tables, heads, kv_heads, head_dim, page, head_dim ** -0.5,
+                                   win, part_o, part_ml, n_chunks, n_chunks, **ep)
+            else:
+                K.attention_prefill_tc(q, kc, vc, att, work, pos, tables, heads, kv_heads, head_dim, page, head_dim ** -0.5, win, **ep)
+
+        add(f"window attention with sink and gate ({what})", "attention",
+            lambda: attend(window, sink=True, gate=proj3, gate_offset=qkw), att_bytes, att_flops)
+        full_flops = 4.0 * R * sum(p + 1 for p in range(ctx_len - n, ctx_len)) * heads * head_dim
+        full_bytes = R * ctx_len * kv_heads * head_dim * 4 + rows_n * heads * head_dim * 4
+        add(f"attention, Llama ({what})", "", lambda: attend(None), full_bytes, full_flops)
+        gu = torch.randn(rows_n, 4 * D, device=dev)
+        hmid = torch.empty(rows_n, 2 * D, dtype=torch.bfloat16, device=dev)
+        add(f"gated_act relu ({what})", "swiglu", lambda: K.gated_act(gu, hmid, "relu"), rows_n * 2 * D * 10)
+        add(f"swiglu, Llama ({what})", "", lambda: K.swiglu(gu, hmid), rows_n * 2 * D * 10)
+    return rows
+
+
+def run_nipadra(args):
+    """Prefill (one 2,048-token prompt in one step) and decode (batch 8 at context 2,048) throughput of Nipadra models
+    whose layers have the sizes of the Llama-3.2-1B and Llama-3.1-8B shapes (four layers each, random bf16 weights),
+    beside Llama models of the same sizes; then every kernel of the new design alone beside the like kernel of the
+    Llama path. Prints one JSON line."""
+    import torch
+    from geneinfer_b200 import Engine
+    pk = peaks()
+    layers = args.layers or 4
+    context, batch, T = 2048, 8, PREFILL_TOKENS
+    models = []
+    for name, base in (("1b", LLAMA_1B), ("8b", LLAMA_8B)):
+        llama = dict(base, num_hidden_layers=layers, tie_word_embeddings=True)
+        nip = nipadra_config(base["hidden_size"], base["intermediate_size"], layers, base["vocab_size"],
+                             base["num_attention_heads"], base["head_dim"], base["num_key_value_heads"], 1024)
+        for arch, cfg in (("Llama", llama), ("Nipadra", nip)):
+            if arch == "Llama":
+                folder = model_folder(cfg)
+            else:
+                from geneinfer_b200.weights import write_random_model
+                folder = os.path.join(tempfile.gettempdir(), f"geneinfer_bench_nipadra_{name}_{layers}_{os.getuid()}")
+                if not os.path.isfile(os.path.join(folder, "done")):
+                    write_random_model(cfg, 1, folder, "bfloat16", std=0.02)
+                    open(os.path.join(folder, "done"), "w").close()
+            llm = Engine(folder, dtype="bfloat16", max_seq_len=context, page_size=PAGE, kv_pages=batch * (context // PAGE),
+                         max_running=batch, step_tokens=T, prefix_cache=False)
+            vocab = base["vocab_size"]
+            ms_prefill = time_prefill(llm.steps, T, 2, vocab)
+            ms_decode, _ = time_decode_device(llm.steps, batch, context, args.steps, args.warmup, vocab)
+            llm.steps.check_status()
+            models.append({"model": f"{arch} at the {SHAPES[name][0]} layer sizes, {layers} layers",
+                           "prefill_2048_tok_s": round(T / ms_prefill * 1e3, 1), "prefill_ms": round(ms_prefill, 3),
+                           "decode_b8_ctx2048_tok_s": round(batch / ms_decode * 1e3, 1), "decode_ms_per_step": round(ms_decode, 4),
+                           "weight_gb": round(llm.model.weight_bytes() / 1e9, 3)})
+            del llm
+            torch.cuda.empty_cache()
+    table = nipadra_kernel_table(2048, 32, 8, 64, 1024, T, pk)
+    print(json.dumps({"metric": "Nipadra beside Llama at equal layer sizes (random bf16 weights)", "impl": "ours", "n_gpus": 1,
+                      "dtype": "bf16", "steps": args.steps, "warmup": args.warmup, "peaks": pk["source"],
+                      "peak_gb_s": pk["hbm_gbs"], "peak_tflops": pk["bf16_tflops"], "models": models, "kernels": table}))
+    return 0
+
+
 def run_scenario(args):
     """Two workloads through the entry point, beside the default run: ``mixed`` (32 requests with
     prompts of 128 to 4096 random ids and 256 generated tokens each, admitted together, prompts cut
@@ -595,7 +780,7 @@ def main():
     ap.add_argument("--shape", choices=sorted(SHAPES), default="1b", help="layer sizes (the default is the baseline's third configuration)")
     ap.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16",
                     help="precision of a --scenario run (float32: the requests run alone must give identical tokens)")
-    ap.add_argument("--scenario", choices=["mixed", "prefix", "sizes"], default="",
+    ap.add_argument("--scenario", choices=["mixed", "prefix", "sizes", "nipadra"], default="",
                     help="a workload through the scheduler (mixed, prefix) or decode steps at a grid of sizes, instead of the default run")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -606,6 +791,8 @@ def main():
     args.warmup = max(3, args.warmup)
     if args.scenario == "sizes":
         return run_sizes(args)
+    if args.scenario == "nipadra":
+        return run_nipadra(args)
     if args.scenario:
         return run_scenario(args)
     return run_ours(args)

@@ -406,7 +406,8 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
                             const int* __restrict__ row_req, const int* __restrict__ positions,
                             const int* __restrict__ block_tables, int table_stride, int H, int Hkv, int page_size,
                             float scale_log2, int window, float* __restrict__ part_o, float* __restrict__ part_ml,
-                            int max_chunks, int n_chunks, __nv_bfloat16* __restrict__ out, int* status, int stream_kv) {
+                            int max_chunks, int n_chunks, __nv_bfloat16* __restrict__ out, int* status, int stream_kv,
+                            const AttEpilogue ep) {
     using Cfg = DecodeTma<HD>;
     uint64_t stream_policy;
     asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(stream_policy));
@@ -609,6 +610,13 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
                 const int row = r0 + 8 * r;
                 if (row >= G) continue;
                 __nv_bfloat16* dst = out + (static_cast<size_t>(ci.t) * H + ci.g * G + row) * HD + (lane & 3) * 2;
+                if (!ep.plain()) {
+                    const float f = att_finish(ep, l[r], m[r], ci.t, ci.g * G + row);
+#pragma unroll
+                    for (int n = 0; n < HD / 8; ++n)
+                        *reinterpret_cast<__nv_bfloat162*>(dst + n * 8) = __floats2bfloat162_rn(o[n][2 * r] * f, o[n][2 * r + 1] * f);
+                    continue;
+                }
 #pragma unroll
                 for (int n = 0; n < HD / 8; ++n)
                     *reinterpret_cast<__nv_bfloat162*>(dst + n * 8) = __floats2bfloat162_rn(o[n][2 * r] / l[r], o[n][2 * r + 1] / l[r]);
@@ -646,7 +654,8 @@ constexpr int kCombineMaxDims = 4;                 // head dims per lane: the he
 __global__ void __launch_bounds__(kCombineWarps * 32)
 attention_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                          const int* __restrict__ rows, const int* __restrict__ positions,
-                         __nv_bfloat16* __restrict__ out, int H, int HD, int max_chunks, int window, int skip_single) {
+                         __nv_bfloat16* __restrict__ out, int H, int HD, int max_chunks, int window, int skip_single,
+                         const AttEpilogue ep) {
     __shared__ float s_acc[kCombineWarps][kCombineMaxDims * 32];
     __shared__ float s_l[kCombineWarps];
     const int h = blockIdx.x, idx = blockIdx.y;
@@ -696,11 +705,12 @@ attention_combine_kernel(const float* __restrict__ part_o, const float* __restri
     float total = 0.f;
 #pragma unroll
     for (int w = 0; w < kCombineWarps; ++w) total += s_l[w];
+    const float f = ep.plain() ? 0.f : att_finish(ep, total, M, t, h);
     for (int d = threadIdx.x; d < HD; d += kCombineWarps * 32) {
         float o = 0.f;
 #pragma unroll
         for (int w = 0; w < kCombineWarps; ++w) o += s_acc[w][d];
-        out[(static_cast<size_t>(t) * H + h) * HD + d] = __float2bfloat16_rn(o / total);
+        out[(static_cast<size_t>(t) * H + h) * HD + d] = __float2bfloat16_rn(ep.plain() ? o / total : o * f);
     }
 }
 
@@ -835,7 +845,7 @@ attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __
                              const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ out,
                              const int* __restrict__ work, const int* __restrict__ positions,
                              const int* __restrict__ block_tables, int table_stride, int H, int Hkv, int page_size,
-                             float scale_log2, int window, int* status) {
+                             float scale_log2, int window, int* status, const AttEpilogue ep) {
     using Cfg = PrefillTma<HD>;
     constexpr int kTile = Cfg::kTile, kStages = Cfg::kStages;
     extern __shared__ uint8_t smem_raw[];
@@ -983,7 +993,7 @@ attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __
         const int row = warp * 16 + (lane >> 2) + r * 8;
         if (row >= n_rows) continue;
         const int tok = row / G, hh = row % G;
-        const float inv = 1.0f / l[r];
+        const float inv = ep.plain() ? 1.0f / l[r] : att_finish(ep, l[r], m[r], t0 + tok, g * G + hh);
         __nv_bfloat16* dst = out + (static_cast<size_t>(t0 + tok) * H + g * G + hh) * HD + (lane & 3) * 2;
 #pragma unroll
         for (int n = 0; n < HD / 8; ++n)
@@ -995,7 +1005,7 @@ template <int HD>
 static int launch_decode(const void* q, const void* kc, const void* vc, void* out, const int* rows, int n_rows,
                          const int* row_req, const int* positions, const int* tables, int table_stride, int H, int Hkv,
                          int page_size, float scale, int window, float* part_o, float* part_ml, int max_chunks,
-                         int n_chunks, cudaStream_t st) {
+                         int n_chunks, const AttEpilogue ep, cudaStream_t st) {
     constexpr int smem = 16 * HD * 2 + 4 * 2 * kTileKeys * HD * 2;
     constexpr int red = 4 * 16 * (HD + 2) * 4;
     constexpr int bytes = smem > red ? smem : red;
@@ -1012,7 +1022,7 @@ static int launch_decode(const void* q, const void* kc, const void* vc, void* ou
     if (check_launch("attention_decode")) return 1;
     dim3 grid2(H, n_rows);
     launch_kernel((attention_combine_kernel), dim3(grid2), dim3(kCombineWarps * 32), 0, st, part_o, part_ml, rows, positions,
-                                                                   static_cast<__nv_bfloat16*>(out), H, HD, max_chunks, window, 0);
+                                                                   static_cast<__nv_bfloat16*>(out), H, HD, max_chunks, window, 0, ep);
     return check_launch("attention_combine");
 }
 
@@ -1022,7 +1032,7 @@ template <int HD>
 static int launch_decode_tma(const void* q, const void* kc, const void* vc, void* out, const int* rows, int n_rows,
                              const int* row_req, const int* positions, const int* tables, int table_stride, int H, int Hkv,
                              int page_size, float scale, int window, float* part_o, float* part_ml, int max_chunks,
-                             int n_chunks, long long n_pages, int* status, cudaStream_t st) {
+                             int n_chunks, long long n_pages, int* status, const AttEpilogue ep, cudaStream_t st) {
     using Cfg = DecodeTma<HD>;
     static bool configured = false;
     if (!configured) {
@@ -1047,17 +1057,17 @@ static int launch_decode_tma(const void* q, const void* kc, const void* vc, void
         launch_kernel((attention_decode_tma_kernel<HD, true>), dim3(grid), dim3(Cfg::kThreads), Cfg::kSmemBytes, st, mk, mv,
                   static_cast<const __nv_bfloat16*>(q), rows, n_rows, row_req, positions, tables, table_stride, H, Hkv,
                   page_size, scale * kLog2e, window, part_o, part_ml, max_chunks, n_chunks, static_cast<__nv_bfloat16*>(out), status,
-                  (g_stream_kv && n_rows <= 32) ? 1 : 0);     // measured: 2 % faster at 8 requests, no gain at 64
+                  (g_stream_kv && n_rows <= 32) ? 1 : 0, ep);     // (evict-first) measured: 2 % faster at 8 requests, no gain at 64
     else
         launch_kernel((attention_decode_tma_kernel<HD, false>), dim3(grid), dim3(Cfg::kThreads), Cfg::kSmemBytes, st, mk, mv,
                   static_cast<const __nv_bfloat16*>(q), rows, n_rows, row_req, positions, tables, table_stride, H, Hkv,
                   page_size, scale * kLog2e, window, part_o, part_ml, max_chunks, n_chunks, static_cast<__nv_bfloat16*>(out), status,
-                  (g_stream_kv && n_rows <= 32) ? 1 : 0);     // measured: 2 % faster at 8 requests, no gain at 64
+                  (g_stream_kv && n_rows <= 32) ? 1 : 0, ep);     // (evict-first) measured: 2 % faster at 8 requests, no gain at 64
     if (check_launch("attention_decode_tma")) return 1;
     if (n_chunks == 1) return 0;                     // every token's keys lie in one chunk: nothing to merge
     dim3 grid2(H, n_rows);
     launch_kernel((attention_combine_kernel), dim3(grid2), dim3(kCombineWarps * 32), 0, st, part_o, part_ml, rows, positions,
-                  static_cast<__nv_bfloat16*>(out), H, HD, max_chunks, window, 1);
+                  static_cast<__nv_bfloat16*>(out), H, HD, max_chunks, window, 1, ep);
     return check_launch("attention_combine");
 }
 
@@ -1082,7 +1092,7 @@ static int launch_prefill(const void* q, const void* kc, const void* vc, void* o
 template <int HD>
 static int launch_prefill_tma(const void* q, const void* kc, const void* vc, void* out, const int* work, int n_work,
                               const int* positions, const int* tables, int table_stride, int H, int Hkv, int page_size,
-                              float scale, int window, long long n_pages, int* status, cudaStream_t st) {
+                              float scale, int window, long long n_pages, int* status, const AttEpilogue ep, cudaStream_t st) {
     using Cfg = PrefillTma<HD>;
     static bool configured = false;
     if (!configured) {
@@ -1100,7 +1110,7 @@ static int launch_prefill_tma(const void* q, const void* kc, const void* vc, voi
     dim3 grid(Hkv, n_work);
     launch_kernel((attention_prefill_tma_kernel<HD>), dim3(grid), dim3(Cfg::kThreads), Cfg::kSmemBytes, st, mk, mv,
                   static_cast<const __nv_bfloat16*>(q), static_cast<__nv_bfloat16*>(out), work, positions, tables,
-                  table_stride, H, Hkv, page_size, scale * kLog2e, window, status);
+                  table_stride, H, Hkv, page_size, scale * kLog2e, window, status, ep);
     return check_launch("attention_prefill_tma");
 }
 
@@ -1138,8 +1148,10 @@ static int gi_attention_decode_impl(const void* q, const void* k_cache, const vo
                                    int n_rows, const int* row_req, const int* positions, const int* block_tables,
                                    int table_stride, int H, int Hkv, int hd, int page_size, float scale, int window,
                                    float* part_o, float* part_ml, int max_chunks, int n_chunks, long long n_pages,
-                                   void* status, void* stream) {
+                                   void* status, int sink, const float* gate, int gate_ld, int gate_off, float out_scale,
+                                   void* stream) {
     if (n_rows == 0) return 0;
+    const AttEpilogue ep{sink, gate, gate_ld, gate_off, out_scale};
     GI_REQUIRE(gi_attention_fast_supported(hd, H, Hkv), "attention_decode: head size %d with %d/%d heads is not built", hd, H, Hkv);
     GI_REQUIRE(n_chunks >= 1 && n_chunks <= max_chunks, "attention_decode: %d chunks exceed the workspace's %d", n_chunks, max_chunks);
     GI_REQUIRE(n_rows <= 65535 && Hkv <= 65535, "attention_decode: grid too large");
@@ -1151,7 +1163,7 @@ static int gi_attention_decode_impl(const void* q, const void* k_cache, const vo
                         reinterpret_cast<uintptr_t>(k_cache) % 16 == 0 && reinterpret_cast<uintptr_t>(v_cache) % 16 == 0;
     if (tma_ok) {
 #define GI_DECODE_TMA(HD) return launch_decode_tma<HD>(q, k_cache, v_cache, out, rows, n_rows, row_req, positions, block_tables, \
-        table_stride, H, Hkv, page_size, scale, window, part_o, part_ml, max_chunks, n_chunks, n_pages, static_cast<int*>(status), st)
+        table_stride, H, Hkv, page_size, scale, window, part_o, part_ml, max_chunks, n_chunks, n_pages, static_cast<int*>(status), ep, st)
         switch (hd) {
             case 16: GI_DECODE_TMA(16);
             case 32: GI_DECODE_TMA(32);
@@ -1161,7 +1173,7 @@ static int gi_attention_decode_impl(const void* q, const void* k_cache, const vo
 #undef GI_DECODE_TMA
     }
 #define GI_DECODE(HD) return launch_decode<HD>(q, k_cache, v_cache, out, rows, n_rows, row_req, positions, block_tables, \
-                                               table_stride, H, Hkv, page_size, scale, window, part_o, part_ml, max_chunks, n_chunks, st)
+                                               table_stride, H, Hkv, page_size, scale, window, part_o, part_ml, max_chunks, n_chunks, ep, st)
     switch (hd) {
         case 16: GI_DECODE(16);
         case 32: GI_DECODE(32);
@@ -1175,14 +1187,16 @@ static int gi_attention_decode_impl(const void* q, const void* k_cache, const vo
 static int gi_attention_prefill_impl(const void* q, const void* k_cache, const void* v_cache, void* out, const int* work,
                                     int n_work, const int* positions, const int* block_tables, int table_stride, int H,
                                     int Hkv, int hd, int page_size, float scale, int window, long long n_pages,
-                                    void* status, void* stream) {
+                                    void* status, int sink, const float* gate, int gate_ld, int gate_off, float out_scale,
+                                    void* stream) {
     if (n_work == 0) return 0;
+    const AttEpilogue ep{sink, gate, gate_ld, gate_off, out_scale};
     GI_REQUIRE(gi_attention_fast_supported(hd, H, Hkv), "attention_prefill: head size %d with %d/%d heads is not built", hd, H, Hkv);
     GI_REQUIRE(n_work <= 65535, "attention_prefill: %d work items exceed the grid limit 65535", n_work);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (gi_attention_prefill_rows(page_size, hd) == 128 && status != nullptr) {
 #define GI_PREFILL_TMA(HD) return launch_prefill_tma<HD>(q, k_cache, v_cache, out, work, n_work, positions, block_tables, \
-        table_stride, H, Hkv, page_size, scale, window, n_pages, static_cast<int*>(status), st)
+        table_stride, H, Hkv, page_size, scale, window, n_pages, static_cast<int*>(status), ep, st)
         switch (hd) {
             case 16: GI_PREFILL_TMA(16);
             case 32: GI_PREFILL_TMA(32);
@@ -1191,6 +1205,7 @@ static int gi_attention_prefill_impl(const void* q, const void* k_cache, const v
         }
 #undef GI_PREFILL_TMA
     }
+    GI_REQUIRE(ep.plain(), "attention_prefill: a sink, a gate or an output factor needs pages that TMA boxes can tile (page size %d)", page_size);
 #define GI_PREFILL(HD) return launch_prefill<HD>(q, k_cache, v_cache, out, work, n_work, positions, block_tables, table_stride, \
                                                  H, Hkv, page_size, scale, window, st)
     switch (hd) {
@@ -1204,10 +1219,10 @@ static int gi_attention_prefill_impl(const void* q, const void* k_cache, const v
 
 // The exported names: each runs its implementation above and, while a launch program is recorded, leaves a copy of
 // its arguments in the program (common.cuh).
-extern "C" int gi_attention_decode(const void* q, const void* k_cache, const void* v_cache, void* out, const int* rows, int n_rows, const int* row_req, const int* positions, const int* block_tables, int table_stride, int H, int Hkv, int hd, int page_size, float scale, int window, float* part_o, float* part_ml, int max_chunks, int n_chunks, long long n_pages, void* status, void* stream) {
-    return gi::dispatch(gi_attention_decode_impl, q, k_cache, v_cache, out, rows, n_rows, row_req, positions, block_tables, table_stride, H, Hkv, hd, page_size, scale, window, part_o, part_ml, max_chunks, n_chunks, n_pages, status, stream);
+extern "C" int gi_attention_decode(const void* q, const void* k_cache, const void* v_cache, void* out, const int* rows, int n_rows, const int* row_req, const int* positions, const int* block_tables, int table_stride, int H, int Hkv, int hd, int page_size, float scale, int window, float* part_o, float* part_ml, int max_chunks, int n_chunks, long long n_pages, void* status, int sink, const float* gate, int gate_ld, int gate_off, float out_scale, void* stream) {
+    return gi::dispatch(gi_attention_decode_impl, q, k_cache, v_cache, out, rows, n_rows, row_req, positions, block_tables, table_stride, H, Hkv, hd, page_size, scale, window, part_o, part_ml, max_chunks, n_chunks, n_pages, status, sink, gate, gate_ld, gate_off, out_scale, stream);
 }
 
-extern "C" int gi_attention_prefill(const void* q, const void* k_cache, const void* v_cache, void* out, const int* work, int n_work, const int* positions, const int* block_tables, int table_stride, int H, int Hkv, int hd, int page_size, float scale, int window, long long n_pages, void* status, void* stream) {
-    return gi::dispatch(gi_attention_prefill_impl, q, k_cache, v_cache, out, work, n_work, positions, block_tables, table_stride, H, Hkv, hd, page_size, scale, window, n_pages, status, stream);
+extern "C" int gi_attention_prefill(const void* q, const void* k_cache, const void* v_cache, void* out, const int* work, int n_work, const int* positions, const int* block_tables, int table_stride, int H, int Hkv, int hd, int page_size, float scale, int window, long long n_pages, void* status, int sink, const float* gate, int gate_ld, int gate_off, float out_scale, void* stream) {
+    return gi::dispatch(gi_attention_prefill_impl, q, k_cache, v_cache, out, work, n_work, positions, block_tables, table_stride, H, Hkv, hd, page_size, scale, window, n_pages, status, sink, gate, gate_ld, gate_off, out_scale, stream);
 }

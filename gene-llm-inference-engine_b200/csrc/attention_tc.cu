@@ -187,7 +187,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
                             const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ out,
                             const int* __restrict__ work, const int* __restrict__ positions,
                             const int* __restrict__ block_tables, int table_stride, int H, int Hkv, int page_size,
-                            float scale_log2, int window, int* status) {
+                            float scale_log2, int window, int* status, const AttEpilogue ep) {
     using C = Cfg<HD, KEYS>;
     extern __shared__ __align__(1024) uint8_t smem[];
     if (smem_u32(smem) & 1023u) {                                  // the swizzled tiles need 1024-byte alignment
@@ -494,7 +494,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
         }
         if (ok && mbar_wait(smem_u32(&bars[kODone]), (n_tiles - 1) & 1, abort_flag)) {
             tc_fence_after();
-            const float inv = 1.0f / l;
+            // (a row beyond the tile's rows has seen no key: its sum is 0 and nothing of it is stored)
+            const float inv = (ep.plain() || !row_valid) ? 1.0f / l : att_finish(ep, l, m_ref, t0 + tok, g * G + hh);
             __nv_bfloat16* dst = out + (static_cast<size_t>(t0 + tok) * H + g * G + hh) * HD;
 #pragma unroll 1
             for (int c = 0; c < HD / 32; ++c) {
@@ -532,7 +533,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
 template <int HD, int KEYS>
 static int launch(const void* q, const void* kc, const void* vc, void* out, const int* work, int n_work,
                   const int* positions, const int* tables, int table_stride, int H, int Hkv, int page_size, float scale,
-                  int window, long long n_pages, int* status, cudaStream_t st) {
+                  int window, long long n_pages, int* status, const AttEpilogue ep, cudaStream_t st) {
     using C = Cfg<HD, KEYS>;
     static bool configured = false;
     if (!configured) {
@@ -550,7 +551,7 @@ static int launch(const void* q, const void* kc, const void* vc, void* out, cons
     dim3 grid(Hkv, n_work);
     launch_kernel((attention_prefill_tc_kernel<HD, KEYS>), dim3(grid), dim3(kThreads), C::kSmemBytes, st, mk, mv,
                   static_cast<const __nv_bfloat16*>(q), static_cast<__nv_bfloat16*>(out), work, positions, tables,
-                  table_stride, H, Hkv, page_size, scale * kLog2e, window, status);
+                  table_stride, H, Hkv, page_size, scale * kLog2e, window, status, ep);
     return check_launch("attention_prefill_tc");
 }
 
@@ -572,15 +573,17 @@ extern "C" int gi_attention_prefill_tc_supported(int hd, int H, int Hkv, int pag
 static int gi_attention_prefill_tc_impl(const void* q, const void* k_cache, const void* v_cache, void* out, const int* work,
                                        int n_work, const int* positions, const int* block_tables, int table_stride, int H,
                                        int Hkv, int hd, int page_size, float scale, int window, long long n_pages,
-                                       void* status, void* stream) {
+                                       void* status, int sink, const float* gate, int gate_ld, int gate_off, float out_scale,
+                                       void* stream) {
     if (n_work == 0) return 0;
+    const AttEpilogue ep{sink, gate, gate_ld, gate_off, out_scale};
     GI_REQUIRE(gi_attention_prefill_tc_supported(hd, H, Hkv, page_size), "attention_prefill_tc: shape not supported");
     GI_REQUIRE(status != nullptr, "attention_prefill_tc: a status word is required");
     GI_REQUIRE(n_work <= 65535, "attention_prefill_tc: %d work items exceed the grid limit 65535", n_work);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
 #define GI_ATC_LAUNCH(HD_, KEYS_)                                                                                          \
     atc::launch<HD_, KEYS_>(q, k_cache, v_cache, out, work, n_work, positions, block_tables, table_stride, H, Hkv, page_size, \
-                            scale, window, n_pages, static_cast<int*>(status), st)
+                            scale, window, n_pages, static_cast<int*>(status), ep, st)
     // Keys per tile: 128 at head size 64; 64 at head size 128, where a CTA with 128-key tiles needs 192 KB of shared memory
     // and has an SM to itself, while two CTAs with 64-key tiles (112 KB each) overlap one's softmax with the other's
     // MMAs as at head size 64: 642 against 511 TFLOP/s at 8,192 tokens, 374 against 338 at 2,048 (24:8 heads).
@@ -592,6 +595,6 @@ static int gi_attention_prefill_tc_impl(const void* q, const void* k_cache, cons
 
 // The exported names: each runs its implementation above and, while a launch program is recorded, leaves a copy of
 // its arguments in the program (common.cuh).
-extern "C" int gi_attention_prefill_tc(const void* q, const void* k_cache, const void* v_cache, void* out, const int* work, int n_work, const int* positions, const int* block_tables, int table_stride, int H, int Hkv, int hd, int page_size, float scale, int window, long long n_pages, void* status, void* stream) {
-    return gi::dispatch(gi_attention_prefill_tc_impl, q, k_cache, v_cache, out, work, n_work, positions, block_tables, table_stride, H, Hkv, hd, page_size, scale, window, n_pages, status, stream);
+extern "C" int gi_attention_prefill_tc(const void* q, const void* k_cache, const void* v_cache, void* out, const int* work, int n_work, const int* positions, const int* block_tables, int table_stride, int H, int Hkv, int hd, int page_size, float scale, int window, long long n_pages, void* status, int sink, const float* gate, int gate_ld, int gate_off, float out_scale, void* stream) {
+    return gi::dispatch(gi_attention_prefill_tc_impl, q, k_cache, v_cache, out, work, n_work, positions, block_tables, table_stride, H, Hkv, hd, page_size, scale, window, n_pages, status, sink, gate, gate_ld, gate_off, out_scale, stream);
 }

@@ -87,6 +87,24 @@ enum TimelineKernel : int {
 
 __device__ __forceinline__ void pdl_prologue() { pdl_launch_dependents(); pdl_wait(); }
 
+// What an attention kernel does to a finished row besides dividing by the softmax's sum: ``sink`` adds the weight of
+// one more key of score 0 (which has no value) to the sum, ``gate`` multiplies head h's output by
+// sigmoid(gate[t * gate_ld + gate_off + h]) (32-bit), ``out_scale`` by a constant. plain(): none of these.
+struct AttEpilogue {
+    int sink;
+    const float* gate;
+    int gate_ld, gate_off;
+    float out_scale;
+    __host__ __device__ bool plain() const { return !sink && gate == nullptr && out_scale == 1.0f; }
+};
+// The factor on the unnormalised output of row (t, h) whose weights are exp2(score - m_log2) and sum to l.
+__device__ __forceinline__ float att_finish(const AttEpilogue& e, float l, float m_log2, int t, int h) {
+    if (e.sink) l += exp2f(-m_log2);
+    float f = e.out_scale / l;
+    if (e.gate) f *= 1.0f / (1.0f + expf(-e.gate[static_cast<size_t>(t) * e.gate_ld + e.gate_off + h]));
+    return f;
+}
+
 template <typename... KArgs, typename... Args>
 inline void launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
     cudaLaunchConfig_t cfg = {};

@@ -367,6 +367,20 @@ def attention_generic(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Ten
         0 if gate is None else gate.shape[1], int(gate_offset), float(out_scale), _stream()), "attention")
 
 
+def _epilogue(sink: bool, gate: Optional[torch.Tensor], gate_offset: int, out_scale: float, num_heads: int):
+    """The arguments every attention entry point takes for what follows the softmax: a sink in the denominator,
+    a sigmoid gate per head read from a 32-bit [T, ld] tensor, a constant factor."""
+    if gate is not None and (gate.dim() != 2 or gate_offset < 0 or gate_offset + num_heads > gate.shape[1]):
+        raise KernelError("attention: the gate must be [T, ld] with the heads' columns inside a row")
+    return (int(bool(sink)), _opt(gate, "gate", torch.float32), 0 if gate is None else gate.shape[1], int(gate_offset),
+            float(out_scale))
+
+
+def attention_tma_pages(page_size: int) -> bool:
+    """Whether the TMA-fed attention kernels can tile pages of this size."""
+    return page_size % 8 == 0 and (32 % page_size == 0 or page_size % 32 == 0)
+
+
 def attention_supported(head_dim: int) -> bool:
     """Whether any attention kernel of the library serves this head size (multiples of 16 up to 256)."""
     return bool(lib().gi_attention_generic_supported(head_dim))
@@ -391,9 +405,11 @@ def attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
                      rows: torch.Tensor, row_req: torch.Tensor, positions: torch.Tensor, block_tables: torch.Tensor,
                      num_heads: int, num_kv_heads: int, head_dim: int, page_size: int, scale: float,
                      window: Optional[int], part_o: torch.Tensor, part_ml: torch.Tensor, max_chunks: int,
-                     n_chunks: int) -> None:
+                     n_chunks: int, sink: bool = False, gate: Optional[torch.Tensor] = None, gate_offset: int = 0,
+                     out_scale: float = 1.0) -> None:
     """Attention of single decoded tokens (bfloat16): ``rows`` lists their step rows; the context is
-    split into fixed chunks whose partial results go through ``part_o`` / ``part_ml``."""
+    split into fixed chunks whose partial results go through ``part_o`` / ``part_ml``. ``sink``, ``gate``,
+    ``gate_offset``, ``out_scale``: as in ``attention_generic``."""
     n = rows.numel()
     if part_o.numel() < n * num_heads * max_chunks * head_dim or part_ml.numel() < n * num_heads * max_chunks * 2:
         raise KernelError("attention_decode: the workspace is too small")
@@ -407,7 +423,8 @@ def attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
         _dev(positions, "positions", torch.int32), _dev(block_tables, "block_tables", torch.int32),
         block_tables.shape[1], num_heads, num_kv_heads, head_dim, page_size, float(scale), int(window or 0),
         _dev(part_o, "part_o", torch.float32), _dev(part_ml, "part_ml", torch.float32), max_chunks, n_chunks,
-        k_cache.shape[0], _tc_state(q.device).status.data_ptr(), _stream()), "attention_decode")
+        k_cache.shape[0], _tc_state(q.device).status.data_ptr(), *_epilogue(sink, gate, gate_offset, out_scale, num_heads),
+        _stream()), "attention_decode")
     tma = page_size % 8 == 0 and (32 % page_size == 0 or page_size % 32 == 0)
     if n_chunks > 1 or not tma:
         count_launches(1)     # the kernel that merges the chunks (not needed when every context is one chunk)
@@ -415,7 +432,9 @@ def attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
 
 def attention_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor,
                       work: torch.Tensor, positions: torch.Tensor, block_tables: torch.Tensor, num_heads: int,
-                      num_kv_heads: int, head_dim: int, page_size: int, scale: float, window: Optional[int]) -> None:
+                      num_kv_heads: int, head_dim: int, page_size: int, scale: float, window: Optional[int],
+                      sink: bool = False, gate: Optional[torch.Tensor] = None, gate_offset: int = 0,
+                      out_scale: float = 1.0) -> None:
     """Attention of prompt portions (bfloat16): ``work`` [n, 3] = (first step row of a tile, tokens
     in it (at most attention_prefill_rows() // group size), request index)."""
     if work.dim() != 2 or work.shape[1] != 3:
@@ -429,7 +448,8 @@ def attention_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Ten
         _dev(out, "out", torch.bfloat16), _dev(work, "work", torch.int32), work.shape[0],
         _dev(positions, "positions", torch.int32), _dev(block_tables, "block_tables", torch.int32),
         block_tables.shape[1], num_heads, num_kv_heads, head_dim, page_size, float(scale), int(window or 0),
-        k_cache.shape[0], _tc_state(q.device).status.data_ptr(), _stream()), "attention_prefill")
+        k_cache.shape[0], _tc_state(q.device).status.data_ptr(), *_epilogue(sink, gate, gate_offset, out_scale, num_heads),
+        _stream()), "attention_prefill")
 
 
 def attention_prefill_tc_supported(head_dim: int, num_heads: int, num_kv_heads: int, page_size: int) -> bool:
@@ -439,7 +459,9 @@ def attention_prefill_tc_supported(head_dim: int, num_heads: int, num_kv_heads: 
 
 def attention_prefill_tc(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor,
                          work: torch.Tensor, positions: torch.Tensor, block_tables: torch.Tensor, num_heads: int,
-                         num_kv_heads: int, head_dim: int, page_size: int, scale: float, window: Optional[int]) -> None:
+                         num_kv_heads: int, head_dim: int, page_size: int, scale: float, window: Optional[int],
+                         sink: bool = False, gate: Optional[torch.Tensor] = None, gate_offset: int = 0,
+                         out_scale: float = 1.0) -> None:
     """Attention of prompt portions on the tcgen05 tensor cores: ``work`` [n, 3] = (first step row of
     a tile, tokens in it (at most 128 // group size), request index)."""
     if work.dim() != 2 or work.shape[1] != 3:
@@ -453,7 +475,8 @@ def attention_prefill_tc(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.
         _dev(out, "out", torch.bfloat16), _dev(work, "work", torch.int32), work.shape[0],
         _dev(positions, "positions", torch.int32), _dev(block_tables, "block_tables", torch.int32),
         block_tables.shape[1], num_heads, num_kv_heads, head_dim, page_size, float(scale), int(window or 0),
-        k_cache.shape[0], _tc_state(q.device).status.data_ptr(), _stream()), "attention_prefill_tc")
+        k_cache.shape[0], _tc_state(q.device).status.data_ptr(), *_epilogue(sink, gate, gate_offset, out_scale, num_heads),
+        _stream()), "attention_prefill_tc")
 
 
 def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False) -> None:

@@ -76,7 +76,7 @@ class AttentionMixer:
         self.w_o = Linear(weights["w_o"], build.compute_dtype, build.device, tiles=build.weight_tiles)
         self.dtype = build.compute_dtype
         # bfloat16 with a head size the tensor-core kernels are built for; else the general kernel
-        self.fast = self.dtype is torch.bfloat16 and not self.extended and kernels.attention_fast_supported(
+        self.fast = self.dtype is torch.bfloat16 and kernels.attention_fast_supported(
             self.head_dim, self.num_heads, self.num_kv_heads)
         self._prefill_rows = {}
         if self.fast:
@@ -108,13 +108,40 @@ class AttentionMixer:
         """What the mixer's launches depend on besides the token count: whose cache it uses, and (tensor-core
         kernels) how many rows are single decoded tokens, how many tiles the prompt portions make and how many
         chunks the longest context of a single token has. Asking also places this step's work lists on the device."""
-        if not self.fast:
+        if not self._fast_now(ctx):
             return (run.cache_layer, run.writes_cache)
         rows, work, longest = ctx.attention_work(self.prefill_rows(ctx.page_size) // (self.num_heads // self.num_kv_heads))
         return (run.cache_layer, run.writes_cache, rows.numel(), work.shape[0],
                 (longest + self.chunk_keys - 1) // self.chunk_keys)
 
     takes_then = True      # forward accepts ``then``
+
+    def _fast_now(self, ctx) -> bool:
+        """Whether this step's attention runs on the tensor-core kernels: bfloat16 with a head size they are built for;
+        with a sink, a gate or an output factor also pages that their TMA-fed forms can tile."""
+        return self.fast and (not self.extended or kernels.attention_tma_pages(ctx.page_size))
+
+    def _attend(self, ctx, q, k_cache, v_cache, att, tables, **epilogue) -> None:
+        """Attention of the step's rows: single decoded tokens split their context over many CTAs, portions of
+        prompts run tile by tile (tensor cores); else the general kernel. ``epilogue``: sink, gate, gate_offset, out_scale."""
+        H, Hkv, hd = self.num_heads, self.num_kv_heads, self.head_dim
+        if not self._fast_now(ctx):
+            kernels.attention_generic(q, k_cache, v_cache, att, ctx.row_req, ctx.positions, tables, H, Hkv, hd,
+                                      ctx.page_size, self.scale, self.window, **epilogue)
+            return
+        rows, work, longest = ctx.attention_work(self.prefill_rows(ctx.page_size) // (H // Hkv))
+        if rows.numel():
+            n = rows.numel()
+            part_o = ctx.scratch("att_part_o", (n, H * self.max_chunks * hd), torch.float32, capacity=ctx.max_requests)
+            part_ml = ctx.scratch("att_part_ml", (n, H * self.max_chunks * 2), torch.float32, capacity=ctx.max_requests)
+            n_chunks = (longest + self.chunk_keys - 1) // self.chunk_keys
+            kernels.attention_decode(q, k_cache, v_cache, att, rows, ctx.row_req, ctx.positions, tables, H, Hkv, hd,
+                                     ctx.page_size, self.scale, self.window, part_o, part_ml, self.max_chunks, n_chunks,
+                                     **epilogue)
+        if work.shape[0]:
+            prefill = kernels.attention_prefill_tc if self.prefill_on_tcgen05(ctx.page_size) else kernels.attention_prefill
+            prefill(q, k_cache, v_cache, att, work, ctx.positions, tables, H, Hkv, hd, ctx.page_size, self.scale,
+                    self.window, **epilogue)
 
     def forward(self, ctx, run, xn: torch.Tensor, x: torch.Tensor, then=None) -> None:
         """``xn``: normalised input [T, hidden] in the compute dtype; ``x``: the 32-bit residual
@@ -142,29 +169,12 @@ class AttentionMixer:
                                self.position.interleaved, q, k_cache, v_cache, H, Hkv, hd, ctx.page_size,
                                write_kv=run.writes_cache)
         att = ctx.scratch("att", (T, H * hd), self.dtype)
-        if self.fast:
-            # tensor-core kernels: single decoded tokens split their context over many CTAs,
-            # portions of prompts run tile by tile
-            rows, work, longest = ctx.attention_work(self.prefill_rows(ctx.page_size) // (H // Hkv))
-            if rows.numel():
-                n = rows.numel()
-                part_o = ctx.scratch("att_part_o", (n, H * self.max_chunks * hd), torch.float32, capacity=ctx.max_requests)
-                part_ml = ctx.scratch("att_part_ml", (n, H * self.max_chunks * 2), torch.float32, capacity=ctx.max_requests)
-                n_chunks = (longest + self.chunk_keys - 1) // self.chunk_keys
-                kernels.attention_decode(q, k_cache, v_cache, att, rows, ctx.row_req, ctx.positions, tables, H, Hkv, hd,
-                                         ctx.page_size, self.scale, self.window, part_o, part_ml, self.max_chunks, n_chunks)
-            if work.shape[0]:
-                prefill = kernels.attention_prefill_tc if self.prefill_on_tcgen05(ctx.page_size) else kernels.attention_prefill
-                prefill(q, k_cache, v_cache, att, work, ctx.positions, tables, H, Hkv, hd, ctx.page_size, self.scale,
-                        self.window)
-        else:
-            kernels.attention_generic(q, k_cache, v_cache, att, ctx.row_req, ctx.positions, tables, H, Hkv, hd,
-                                      ctx.page_size, self.scale, self.window)
+        self._attend(ctx, q, k_cache, v_cache, att, tables)
         self.w_o.forward(att, x, accumulate=True, then=then)
 
     def _forward_extended(self, ctx, run, xn, x, q, k_cache, v_cache, tables, then) -> None:
-        """The mixer with options: projections to 32-bit, then per head norm, rotation and page store, the
-        general attention kernel with sink and gate, and the output projection."""
+        """The mixer with options: projections to 32-bit, then per head norm, rotation and page store, attention
+        with sink and gate in its epilogue, and the output projection."""
         T = xn.shape[0]
         H, Hkv, hd = self.num_heads, self.num_kv_heads, self.head_dim
         proj = ctx.scratch("att_proj", (T, self.w_qkv.out_features), torch.float32)
@@ -177,7 +187,6 @@ class AttentionMixer:
                                 ctx.row_req, tables, q, k_cache, v_cache, H, Hkv, hd, ctx.page_size,
                                 write_kv=run.writes_cache)
         att = ctx.scratch("att", (T, H * hd), self.dtype)
-        kernels.attention_generic(q, k_cache, v_cache, att, ctx.row_req, ctx.positions, tables, H, Hkv, hd,
-                                  ctx.page_size, self.scale, self.window, sink=self.sink,
-                                  gate=proj if self.head_gate else None, gate_offset=gate_off, out_scale=self.out_scale)
+        self._attend(ctx, q, k_cache, v_cache, att, tables, sink=self.sink, gate=proj if self.head_gate else None,
+                     gate_offset=gate_off, out_scale=self.out_scale)
         self.w_o.forward(att, x, accumulate=True, then=then)
