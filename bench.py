@@ -432,10 +432,17 @@ def nipadra_kernel_table(width, heads, kv_heads, head_dim, window, T, pk):
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
     rows = []
 
-    def add(name, like, fn, nbytes, flops=0.0):
+    props = torch.cuda.get_device_properties(dev)
+    # 32-bit multiply-adds a second on the CUDA cores (128 lanes an SM): the bound of what must stay 32-bit
+    simt_ops = props.multi_processor_count * 128 * 1.965e9
+
+    def add(name, like, fn, nbytes, flops=0.0, simt=0.0):
         ms = time_calls(fn, flush=flush)
         ideal = max(nbytes / (pk["hbm_gbs"] * 1e9), flops / (pk["bf16_tflops"] * 1e12)) * 1e3
-        rows.append({"kernel": name, "like": like, "us": round(ms * 1e3, 1), "frac": round(ideal / ms, 3)})
+        row = {"kernel": name, "like": like, "us": round(ms * 1e3, 1), "frac": round(ideal / ms, 3)}
+        if simt:
+            row["frac_of_32bit_issue"] = round(simt / simt_ops * 1e3 / ms, 3)
+        rows.append(row)
 
     def seg(R, n):
         i32 = dict(dtype=torch.int32, device=dev)
@@ -459,8 +466,13 @@ def nipadra_kernel_table(width, heads, kv_heads, head_dim, window, T, pk):
         s0, sl, slots, rr = seg(R, n)
         decay = torch.full((H,), 0.99, device=dev)
         scan_bytes = rows_n * D * 4 * 4 + 2 * R * H * 128 * 128 * 4
+        parts = {}
+        if rows_n > K.SCAN_PART:        # as the mixers do: long segments are cut into parts that run side by side
+            parts = {"part_len": K.SCAN_PART, "ws_state": torch.empty(K.scan_parts(rows_n, R), D * 128, device=dev),
+                     "ws_decay": torch.empty(rows_n, max(H, D // 64), device=dev)}
         add(f"linear_scan, constant decay ({what})", "attention", lambda: K.linear_scan(
-            proj, 0, proj, D, proj, 2 * D, H, 1, 128, 128, True, state, 0, s0, sl, slots, out, decay=decay), scan_bytes)
+            proj, 0, proj, D, proj, 2 * D, H, 1, 128, 128, True, state, 0, s0, sl, slots, out, decay=decay, **parts), scan_bytes,
+            simt=rows_n * H * 128 * 128 * (4.0 if parts else 3.0))
         y = torch.empty(rows_n, D, dtype=torch.bfloat16, device=dev)
         add(f"gated_group_norm ({what})", "swiglu", lambda: K.gated_group_norm(out, proj, 3 * D, w, y, 1, 1e-6, False), rows_n * D * 10)
         # state space: heads of 64, state 128
@@ -475,7 +487,8 @@ def nipadra_kernel_table(width, heads, kv_heads, head_dim, window, T, pk):
         dtb, alog, skip = torch.zeros(Hs, device=dev), torch.zeros(Hs, device=dev), torch.ones(Hs, device=dev)
         add(f"linear_scan, step sizes ({what})", "attention", lambda: K.linear_scan(
             xbc, D + N, xbc, D, xbc, 0, Hs, Hs, N, 64, False, st2, 0, s0, sl, slots, out, dt=proj2, dt_offset=D + C, dt_bias=dtb,
-            a_log=alog, skip=skip), rows_n * (D * 8 + 2 * N * 4) + 2 * R * Hs * N * 64 * 4)
+            a_log=alog, skip=skip, **parts), rows_n * (D * 8 + 2 * N * 4) + 2 * R * Hs * N * 64 * 4,
+            simt=rows_n * Hs * N * 64 * (4.0 if parts else 3.0))
         # windowed attention: norm + rotation + store, then attention over a context of T
         page = 16
         ctx_len = T

@@ -66,8 +66,15 @@ conv_state_update_kernel(const float* __restrict__ in, int ld, int in_off, float
 }
 
 // ---------------------------------------------------------------------------------- the recurrence
-// A block owns 32 columns of one head's state of one request; kSplit neighbouring lanes share a column, each with
-// kRows of its rows in registers. Tokens are staged kChunk at a time in shared memory (activated, with their a and b).
+// A block owns 32 columns of one head's state of one request, each thread a few rows x 4 columns of it in registers.
+// Tokens are staged a chunk at a time in shared memory (activated, with their a and b).
+//
+// Long segments are cut into parts of part_len tokens that run side by side (kParts): every part starts from a zero
+// state and leaves its own end state U_p and, per token, the product A_t of the decays since the part's start
+// (scan kernel); the parts' true start states follow from S_(p+1) = A_end(p) S_p + U_p, S_0 the request's state
+// (link kernel, a short loop per state element); and every token gets what the start state adds to it,
+// o_t += A_t S_p^T q_t (apply kernel, a small matrix product per part). Steps whose segments all fit one part run
+// the scan kernel alone, straight on the state slot.
 constexpr int kScanCols = 32;
 constexpr int kScanChunk = 16;
 
@@ -83,92 +90,272 @@ struct ScanArgs {
     float* state; long long slot_stride; long long state_off;          // per slot: [H, dk, dv] at state_off
     const int* seg_start; const int* seg_len; const int* state_slots;
     float* out;                                           // [T, H * dv]
+    int part_len, max_parts;                              // kParts: tokens per part, parts per request in the grid
+    float* ws_state;                                      // [parts of the step, H, dk, dv]
+    float* ws_decay;                                      // [T, H]
 };
 
-template <int kRows, int kSplit>
-__global__ void __launch_bounds__(kScanCols * kSplit)
+// Where request r's parts start among the step's parts: the parts of the requests before it.
+__device__ __forceinline__ int parts_before(const ScanArgs& p, int r) {
+    int base = 0;
+    for (int i = 0; i < r; ++i) base += (p.seg_len[i] + p.part_len - 1) / p.part_len;
+    return base;
+}
+
+template <int kDk, int kRT, bool kParts>
+__global__ void __launch_bounds__(kDk / kRT * 8)
 linear_scan_kernel(const ScanArgs p) {
     pdl_prologue();
-    constexpr int kDk = kRows * kSplit;                   // padded state rows
-    __shared__ float s_q[kScanChunk][kDk];
-    __shared__ float s_k[kScanChunk][kDk];
-    __shared__ float s_v[kScanChunk][kScanCols];
-    __shared__ float s_a[kScanChunk], s_b[kScanChunk];
-    const int tile = blockIdx.x, h = blockIdx.y, r = blockIdx.z;
+    // A thread owns kRT rows x 4 columns of the state in registers (thread = row group x column group; a block covers
+    // all kDk padded rows and 32 columns): per token it reads kRT k and q values and 4 v values from shared memory
+    // for 4 kRT state elements. A token's output is the sum over the row groups, added up in their order once per
+    // chunk of tokens.
+    constexpr int kGroups = kDk / kRT;                    // row groups
+    constexpr int kThreads = kGroups * 8;
+    constexpr int kChunk = kDk >= 128 ? kScanChunk / 2 : kScanChunk;      // tokens staged at a time (shared memory)
+    constexpr int kPerThread = kChunk * kDk / kThreads;   // q (and k) values a thread stages per chunk
+    constexpr int kVPerThread = kChunk * kScanCols / kThreads;
+    __shared__ __align__(16) float s_q[kChunk][kDk];
+    __shared__ __align__(16) float s_k[kChunk][kDk];
+    __shared__ __align__(16) float s_v[kChunk][kScanCols];
+    __shared__ __align__(16) float s_o[kChunk][kGroups][kScanCols];
+    __shared__ float s_a[kChunk], s_b[kChunk];
+    const int tile = blockIdx.x, h = blockIdx.y;
+    const int r = kParts ? blockIdx.z / p.max_parts : blockIdx.z;
+    const int part_idx = kParts ? blockIdx.z % p.max_parts : 0;
     const int g = h / p.group;
-    const int col = threadIdx.x / kSplit, part = threadIdx.x % kSplit;
-    const int j = tile * kScanCols + col;                 // column of the state
-    const bool live = j < p.dv;
-    const int n = p.seg_len[r], s0 = p.seg_start[r];
-    float* S = p.state + static_cast<long long>(p.state_slots[r]) * p.slot_stride + p.state_off +
-               static_cast<long long>(h) * p.dk * p.dv;
-    float s[kRows];
+    const int cg = threadIdx.x % 8, rg = threadIdx.x / 8;
+    const int j0 = tile * kScanCols + cg * 4;             // first of this thread's columns
+    int n = p.seg_len[r], s0 = p.seg_start[r];
+    float* S;
+    if (kParts) {
+        if (part_idx * p.part_len >= n) return;
+        s0 += part_idx * p.part_len;
+        n = min(p.part_len, n - part_idx * p.part_len);
+        S = p.ws_state + (static_cast<size_t>(parts_before(p, r) + part_idx) * p.H + h) * p.dk * p.dv;
+    } else {
+        S = p.state + static_cast<long long>(p.state_slots[r]) * p.slot_stride + p.state_off +
+            static_cast<long long>(h) * p.dk * p.dv;
+    }
+    float s[kRT][4];
 #pragma unroll
-    for (int i = 0; i < kRows; ++i) {
-        const int row = part * kRows + i;
-        s[i] = (live && row < p.dk) ? S[static_cast<size_t>(row) * p.dv + j] : 0.f;
+    for (int i = 0; i < kRT; ++i) {
+        const int row = rg * kRT + i;
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+            s[i][c] = (!kParts && row < p.dk && j0 + c < p.dv) ? S[static_cast<size_t>(row) * p.dv + j0 + c] : 0.f;
     }
     const float skip = p.skip ? p.skip[h] : 0.f;
     const float a_const = p.decay ? p.decay[h] : 0.f;
     const float neg_rate = p.decay ? 0.f : -expf(p.a_log[h]);
     const float bias = p.decay ? 0.f : p.dt_bias[h];
-    const int nthreads = kScanCols * kSplit;
-    for (int c0 = 0; c0 < n; c0 += kScanChunk) {
-        const int m = min(kScanChunk, n - c0);
-        __syncthreads();
-        for (int e = threadIdx.x; e < m * kDk; e += nthreads) {
+    float cum = 1.f;                                      // thread 0: product of the decays since the part's start
+    // the loads of a chunk are requested while the chunk before it is worked on
+    float qv[kPerThread], kv[kPerThread], vv[kVPerThread], dt_raw = 0.f;
+    auto request = [&](int c0) {
+        const int m = min(kChunk, n - c0);
+#pragma unroll
+        for (int u = 0; u < kPerThread; ++u) {
+            const int e = threadIdx.x + u * kThreads;
             const int tt = e / kDk, i = e % kDk;
             const size_t t = static_cast<size_t>(s0 + c0 + tt);
-            float qv = 0.f, kv = 0.f;
-            if (i < p.dk) {
-                qv = p.q[t * p.ld_q + p.q_off + g * p.dk + i];
-                kv = p.k[t * p.ld_k + p.k_off + g * p.dk + i];
-                if (p.act) { qv = silu_f(qv); kv = silu_f(kv); }
-            }
-            s_q[tt][i] = qv;
-            s_k[tt][i] = kv;
+            const bool in = tt < m && i < p.dk;
+            qv[u] = in ? p.q[t * p.ld_q + p.q_off + g * p.dk + i] : 0.f;
+            kv[u] = in ? p.k[t * p.ld_k + p.k_off + g * p.dk + i] : 0.f;
         }
-        for (int e = threadIdx.x; e < m * kScanCols; e += nthreads) {
-            const int tt = e / kScanCols, cc = e % kScanCols;
-            const int jj = tile * kScanCols + cc;
-            float vv = 0.f;
-            if (jj < p.dv) {
-                vv = p.v[static_cast<size_t>(s0 + c0 + tt) * p.ld_v + p.v_off + h * p.dv + jj];
-                if (p.act) vv = silu_f(vv);
-            }
-            s_v[tt][cc] = vv;
+#pragma unroll
+        for (int u = 0; u < kVPerThread; ++u) {
+            const int e = threadIdx.x + u * kThreads;
+            const int tt = e / kScanCols, jj = tile * kScanCols + e % kScanCols;
+            vv[u] = (tt < m && jj < p.dv) ? p.v[static_cast<size_t>(s0 + c0 + tt) * p.ld_v + p.v_off + h * p.dv + jj] : 0.f;
+        }
+        if (!p.decay && threadIdx.x < m)
+            dt_raw = p.dt_raw[static_cast<size_t>(s0 + c0 + threadIdx.x) * p.ld_dt + p.dt_off + h];
+    };
+    request(0);
+    for (int c0 = 0; c0 < n; c0 += kChunk) {
+        const int m = min(kChunk, n - c0);
+        __syncthreads();                                  // the chunk before is done with the staging buffers
+#pragma unroll
+        for (int u = 0; u < kPerThread; ++u) {
+            const int e = threadIdx.x + u * kThreads;
+            s_q[e / kDk][e % kDk] = p.act ? silu_f(qv[u]) : qv[u];
+            s_k[e / kDk][e % kDk] = p.act ? silu_f(kv[u]) : kv[u];
+        }
+#pragma unroll
+        for (int u = 0; u < kVPerThread; ++u) {
+            const int e = threadIdx.x + u * kThreads;
+            s_v[e / kScanCols][e % kScanCols] = p.act ? silu_f(vv[u]) : vv[u];
         }
         if (threadIdx.x < m) {
             if (p.decay) {
                 s_a[threadIdx.x] = a_const;
                 s_b[threadIdx.x] = 1.f;
             } else {
-                const float dt = softplus_f(p.dt_raw[static_cast<size_t>(s0 + c0 + threadIdx.x) * p.ld_dt + p.dt_off + h] + bias);
+                const float dt = softplus_f(dt_raw + bias);
                 s_a[threadIdx.x] = expf(neg_rate * dt);
                 s_b[threadIdx.x] = dt;
             }
         }
         __syncthreads();
+        if (c0 + kChunk < n) request(c0 + kChunk);
+        if (kParts && tile == 0 && threadIdx.x == 0) {
+            for (int tt = 0; tt < m; ++tt) {
+                cum *= s_a[tt];
+                p.ws_decay[static_cast<size_t>(s0 + c0 + tt) * p.H + h] = cum;
+            }
+        }
         for (int tt = 0; tt < m; ++tt) {
-            const float a = s_a[tt], vj = s_v[tt][col];
-            const float bv = s_b[tt] * vj;
+            const float a = s_a[tt], b = s_b[tt];
+            const float4 v4 = *reinterpret_cast<const float4*>(&s_v[tt][cg * 4]);
+            const float bv[4] = {b * v4.x, b * v4.y, b * v4.z, b * v4.w};
+            float o[4] = {0.f, 0.f, 0.f, 0.f};
+            const float4* k4 = reinterpret_cast<const float4*>(&s_k[tt][rg * kRT]);
+            const float4* q4 = reinterpret_cast<const float4*>(&s_q[tt][rg * kRT]);
+#pragma unroll
+            for (int i4 = 0; i4 < kRT / 4; ++i4) {
+                const float4 kk = k4[i4], qq = q4[i4];
+                const float kr[4] = {kk.x, kk.y, kk.z, kk.w}, qr[4] = {qq.x, qq.y, qq.z, qq.w};
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        s[4 * i4 + u][c] = fmaf(a, s[4 * i4 + u][c], kr[u] * bv[c]);
+                        o[c] = fmaf(s[4 * i4 + u][c], qr[u], o[c]);
+                    }
+                }
+            }
+            *reinterpret_cast<float4*>(&s_o[tt][rg][cg * 4]) = make_float4(o[0], o[1], o[2], o[3]);
+        }
+        __syncthreads();
+        for (int e = threadIdx.x; e < m * kScanCols; e += kThreads) {
+            const int tt = e / kScanCols, c = e % kScanCols;
+            const int jj = tile * kScanCols + c;
             float o = 0.f;
 #pragma unroll
-            for (int i = 0; i < kRows; ++i) {
-                const int row = part * kRows + i;
-                s[i] = fmaf(a, s[i], s_k[tt][row] * bv);
-                o = fmaf(s[i], s_q[tt][row], o);
-            }
-#pragma unroll
-            for (int w = kSplit / 2; w > 0; w >>= 1) o += __shfl_xor_sync(0xffffffffu, o, w);
-            if (part == 0 && live)
-                p.out[static_cast<size_t>(s0 + c0 + tt) * p.H * p.dv + h * p.dv + j] = fmaf(skip, vj, o);
+            for (int w = 0; w < kGroups; ++w) o += s_o[tt][w][c];
+            if (jj < p.dv)
+                p.out[static_cast<size_t>(s0 + c0 + tt) * p.H * p.dv + h * p.dv + jj] = fmaf(skip, s_v[tt][c], o);
         }
     }
 #pragma unroll
-    for (int i = 0; i < kRows; ++i) {
-        const int row = part * kRows + i;
-        if (live && row < p.dk) S[static_cast<size_t>(row) * p.dv + j] = s[i];
+    for (int i = 0; i < kRT; ++i) {
+        const int row = rg * kRT + i;
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+            if (row < p.dk && j0 + c < p.dv) S[static_cast<size_t>(row) * p.dv + j0 + c] = s[i][c];
+    }
+}
+
+// The parts' start states: one thread per element of a request's state walks over the request's parts.
+__global__ void __launch_bounds__(256)
+scan_link_kernel(const ScanArgs p) {
+    pdl_prologue();
+    const int r = blockIdx.y;
+    const size_t per_head = static_cast<size_t>(p.dk) * p.dv;
+    const size_t e = static_cast<size_t>(blockIdx.x) * 256 + threadIdx.x;
+    if (e >= per_head * p.H) return;
+    const int h = static_cast<int>(e / per_head);
+    const int n = p.seg_len[r], s0 = p.seg_start[r];
+    const int parts = (n + p.part_len - 1) / p.part_len;
+    float* slot = p.state + static_cast<long long>(p.state_slots[r]) * p.slot_stride + p.state_off;
+    float* ws = p.ws_state + static_cast<size_t>(parts_before(p, r)) * p.H * per_head;
+    float S = slot[e];
+    constexpr int kBatch = 8;                             // parts whose loads are in flight together
+    for (int q0 = 0; q0 < parts; q0 += kBatch) {
+        float U[kBatch], A[kBatch];
+#pragma unroll
+        for (int u = 0; u < kBatch; ++u) {
+            const int q = q0 + u;
+            const bool in = q < parts;
+            const int last = s0 + min((q + 1) * p.part_len, n) - 1;
+            U[u] = in ? ws[static_cast<size_t>(q) * p.H * per_head + e] : 0.f;
+            A[u] = in ? p.ws_decay[static_cast<size_t>(last) * p.H + h] : 1.f;
+        }
+#pragma unroll
+        for (int u = 0; u < kBatch; ++u) {
+            if (q0 + u < parts) {
+                ws[static_cast<size_t>(q0 + u) * p.H * per_head + e] = S;      // the state this part starts from
+                S = fmaf(A[u], S, U[u]);
+            }
+        }
+    }
+    slot[e] = S;
+}
+
+// o_t += A_t S_p^T q_t for the tokens of one part, one head and 32 columns: the start state's columns and 16 tokens'
+// queries (transposed) in shared memory, a warp per four tokens, a lane per column.
+template <int kDk>
+__global__ void __launch_bounds__(128)
+scan_apply_kernel(const ScanArgs p) {
+    pdl_prologue();
+    constexpr int kChunk = kDk > 128 ? kScanChunk / 2 : kScanChunk;
+    __shared__ float s_S[kDk][kScanCols];
+    __shared__ __align__(16) float s_qT[kDk][kChunk + 4];      // rows 80 bytes apart: fewer bank conflicts when a chunk is laid down
+    const int tile = blockIdx.x, h = blockIdx.y;
+    const int r = blockIdx.z / p.max_parts, part_idx = blockIdx.z % p.max_parts;
+    const int g = h / p.group;
+    int n = p.seg_len[r], s0 = p.seg_start[r];
+    if (part_idx * p.part_len >= n) return;
+    s0 += part_idx * p.part_len;
+    n = min(p.part_len, n - part_idx * p.part_len);
+    const float* S = p.ws_state + (static_cast<size_t>(parts_before(p, r) + part_idx) * p.H + h) * p.dk * p.dv;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int j = tile * kScanCols + lane;
+    for (int e = threadIdx.x; e < kDk * kScanCols; e += 128) {
+        const int i = e / kScanCols, jj = tile * kScanCols + e % kScanCols;
+        s_S[i][e % kScanCols] = (i < p.dk && jj < p.dv) ? S[static_cast<size_t>(i) * p.dv + jj] : 0.f;
+    }
+    // the queries of a chunk are requested while the chunk before it is worked on
+    constexpr int kPerThread = kChunk * kDk / 128;
+    float qv[kPerThread];
+    auto request = [&](int c0) {
+        const int m = min(kChunk, n - c0);
+#pragma unroll
+        for (int u = 0; u < kPerThread; ++u) {
+            const int e = threadIdx.x + u * 128;
+            const int tt = e / kDk, i = e % kDk;
+            qv[u] = (tt < m && i < p.dk) ? p.q[static_cast<size_t>(s0 + c0 + tt) * p.ld_q + p.q_off + g * p.dk + i] : 0.f;
+        }
+    };
+    request(0);
+    for (int c0 = 0; c0 < n; c0 += kChunk) {
+        const int m = min(kChunk, n - c0);
+        __syncthreads();
+#pragma unroll
+        for (int u = 0; u < kPerThread; ++u) {
+            const int e = threadIdx.x + u * 128;
+            s_qT[e % kDk][e / kDk] = p.act ? silu_f(qv[u]) : qv[u];
+        }
+        __syncthreads();
+        if (c0 + kChunk < n) request(c0 + kChunk);
+        // what the sums are added to, and the decays that scale them, are on their way meanwhile
+        float old[4], dec[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int tt = warp * 4 + u;
+            const bool in = tt < m && j < p.dv;
+            const size_t t = static_cast<size_t>(s0 + c0 + (in ? tt : 0));
+            old[u] = in ? p.out[t * p.H * p.dv + h * p.dv + j] : 0.f;
+            dec[u] = in ? p.ws_decay[t * p.H + h] : 0.f;
+        }
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+        if (warp * 4 < kChunk)
+#pragma unroll 8
+        for (int i = 0; i < kDk; ++i) {
+            const float sv = s_S[i][lane];
+            const float4 q4 = *reinterpret_cast<const float4*>(&s_qT[i][warp * 4]);
+            acc[0] = fmaf(q4.x, sv, acc[0]);
+            acc[1] = fmaf(q4.y, sv, acc[1]);
+            acc[2] = fmaf(q4.z, sv, acc[2]);
+            acc[3] = fmaf(q4.w, sv, acc[3]);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int tt = warp * 4 + u;
+            if (tt < m && j < p.dv)
+                p.out[static_cast<size_t>(s0 + c0 + tt) * p.H * p.dv + h * p.dv + j] = fmaf(dec[u], acc[u], old[u]);
+        }
     }
 }
 
@@ -230,33 +417,48 @@ static int gi_causal_conv_impl(const float* in, int ld, int in_off, const float*
     return check_launch("causal_conv");
 }
 
-template <int kRows, int kSplit>
+template <int kDk, int kRT>
 static void launch_scan(const ScanArgs& a, int R, cudaStream_t st) {
-    dim3 grid((a.dv + kScanCols - 1) / kScanCols, a.H, R);
-    launch_kernel((linear_scan_kernel<kRows, kSplit>), dim3(grid), dim3(kScanCols * kSplit), 0, st, a);
+    const unsigned tiles = (a.dv + kScanCols - 1) / kScanCols;
+    constexpr int kThreads = kDk / kRT * 8;
+    if (a.part_len == 0) {
+        launch_kernel((linear_scan_kernel<kDk, kRT, false>), dim3(tiles, a.H, R), dim3(kThreads), 0, st, a);
+        return;
+    }
+    launch_kernel((linear_scan_kernel<kDk, kRT, true>), dim3(tiles, a.H, R * a.max_parts), dim3(kThreads), 0, st, a);
+    const size_t elements = static_cast<size_t>(a.H) * a.dk * a.dv;
+    launch_kernel((scan_link_kernel), dim3(static_cast<unsigned>((elements + 255) / 256), R), dim3(256), 0, st, a);
+    launch_kernel((scan_apply_kernel<kDk>), dim3(tiles, a.H, R * a.max_parts), dim3(128), 0, st, a);
 }
 
+// part_len 0: every segment is walked from the request's state by one block per head and column tile. Otherwise
+// segments are cut into parts of part_len tokens (at most max_parts per request) that run side by side; ws_state
+// holds [parts of the step, H, dk, dv] floats and ws_decay [T, H].
 static int gi_linear_scan_impl(const float* q, int ld_q, int q_off, const float* k, int ld_k, int k_off, const float* v,
                                int ld_v, int v_off, int H, int group, int dk, int dv, int act, const float* decay,
                                const float* dt_raw, int ld_dt, int dt_off, const float* dt_bias, const float* a_log,
                                const float* skip, float* state, long long slot_stride, long long state_off,
                                const int* seg_start, const int* seg_len, const int* state_slots, float* out, int R,
-                               void* stream) {
+                               int part_len, int max_parts, float* ws_state, float* ws_decay, void* stream) {
     if (R == 0) return 0;
     GI_REQUIRE(R > 0 && H > 0 && dk > 0 && dv > 0 && group > 0, "linear_scan: sizes must be positive");
     GI_REQUIRE(H % group == 0, "linear_scan: %d heads are not a multiple of the group size %d", H, group);
     GI_REQUIRE(dk <= 256, "linear_scan: %d state rows per head exceed 256", dk);
-    GI_REQUIRE(R <= 65535 && H <= 65535, "linear_scan: the grid limit 65535 is exceeded");
     GI_REQUIRE(decay != nullptr || (dt_raw != nullptr && dt_bias != nullptr && a_log != nullptr),
                "linear_scan: neither constant decays nor step sizes are given");
+    GI_REQUIRE(part_len == 0 || (part_len > 0 && max_parts > 0 && ws_state != nullptr && ws_decay != nullptr),
+               "linear_scan: parts need their length, their number and both workspaces");
+    GI_REQUIRE(static_cast<long long>(R) * (part_len ? max_parts : 1) <= 65535 && H <= 65535, "linear_scan: the grid limit 65535 is exceeded");
     ScanArgs a{q, k, v, ld_q, ld_k, ld_v, q_off, k_off, v_off, H, group, dk, dv, act, decay, dt_raw, ld_dt, dt_off, dt_bias,
-               a_log, skip, state, slot_stride, state_off, seg_start, seg_len, state_slots, out};
+               a_log, skip, state, slot_stride, state_off, seg_start, seg_len, state_slots, out, part_len, max_parts, ws_state,
+               ws_decay};
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (dk <= 16) launch_scan<4, 4>(a, R, st);
-    else if (dk <= 32) launch_scan<8, 4>(a, R, st);
-    else if (dk <= 64) launch_scan<16, 4>(a, R, st);
-    else if (dk <= 128) launch_scan<32, 4>(a, R, st);
-    else launch_scan<32, 8>(a, R, st);
+    // (padded state rows, rows per thread)
+    if (dk <= 16) launch_scan<16, 4>(a, R, st);
+    else if (dk <= 32) launch_scan<32, 4>(a, R, st);
+    else if (dk <= 64) launch_scan<64, 8>(a, R, st);
+    else if (dk <= 128) launch_scan<128, 8>(a, R, st);
+    else launch_scan<256, 16>(a, R, st);
     return check_launch("linear_scan");
 }
 
@@ -283,8 +485,8 @@ extern "C" int gi_causal_conv(const float* in, int ld, int in_off, const float* 
     return gi::dispatch(gi_causal_conv_impl, in, ld, in_off, weight, bias, state, slot_stride, state_off, row_req, seg_start, seg_len, state_slots, out, C, taps, T, R, stream);
 }
 
-extern "C" int gi_linear_scan(const float* q, int ld_q, int q_off, const float* k, int ld_k, int k_off, const float* v, int ld_v, int v_off, int H, int group, int dk, int dv, int act, const float* decay, const float* dt_raw, int ld_dt, int dt_off, const float* dt_bias, const float* a_log, const float* skip, float* state, long long slot_stride, long long state_off, const int* seg_start, const int* seg_len, const int* state_slots, float* out, int R, void* stream) {
-    return gi::dispatch(gi_linear_scan_impl, q, ld_q, q_off, k, ld_k, k_off, v, ld_v, v_off, H, group, dk, dv, act, decay, dt_raw, ld_dt, dt_off, dt_bias, a_log, skip, state, slot_stride, state_off, seg_start, seg_len, state_slots, out, R, stream);
+extern "C" int gi_linear_scan(const float* q, int ld_q, int q_off, const float* k, int ld_k, int k_off, const float* v, int ld_v, int v_off, int H, int group, int dk, int dv, int act, const float* decay, const float* dt_raw, int ld_dt, int dt_off, const float* dt_bias, const float* a_log, const float* skip, float* state, long long slot_stride, long long state_off, const int* seg_start, const int* seg_len, const int* state_slots, float* out, int R, int part_len, int max_parts, float* ws_state, float* ws_decay, void* stream) {
+    return gi::dispatch(gi_linear_scan_impl, q, ld_q, q_off, k, ld_k, k_off, v, ld_v, v_off, H, group, dk, dv, act, decay, dt_raw, ld_dt, dt_off, dt_bias, a_log, skip, state, slot_stride, state_off, seg_start, seg_len, state_slots, out, R, part_len, max_parts, ws_state, ws_decay, stream);
 }
 
 extern "C" int gi_gated_group_norm(const float* y, const float* gate, int ld_gate, int gate_off, const float* weight, void* out, int out_dtype, int T, int W, int groups, float eps, int mode, float out_scale, void* stream) {

@@ -55,6 +55,7 @@ class StepContext:
         self.segments = segments
         self.page_size = engine.page_size
         self.max_requests = engine.max_requests
+        self.max_step_tokens = engine.max_step_tokens
         self.max_logit_rows = engine.max_logit_rows
         self.compute_dtype = engine.model.dtype
         self.tokens = views["tokens"]

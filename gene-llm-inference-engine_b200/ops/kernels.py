@@ -286,13 +286,18 @@ def linear_scan(q: torch.Tensor, q_offset: int, k: torch.Tensor, k_offset: int, 
                 seg_start: torch.Tensor, seg_len: torch.Tensor, state_slots: torch.Tensor, out: torch.Tensor,
                 decay: Optional[torch.Tensor] = None, dt: Optional[torch.Tensor] = None, dt_offset: int = 0,
                 dt_bias: Optional[torch.Tensor] = None, a_log: Optional[torch.Tensor] = None,
-                skip: Optional[torch.Tensor] = None) -> None:
+                skip: Optional[torch.Tensor] = None, part_len: int = 0, ws_state: Optional[torch.Tensor] = None,
+                ws_decay: Optional[torch.Tensor] = None) -> None:
     """The recurrence S_t = a_t S_(t-1) + b_t k_t v_t^T, o_t = S_t^T q_t + skip * v_t per head over each
     request's rows in order, the state [H, dk, dv] carried in the request's slot of ``state`` [slots, floats]
     at ``state_offset``. q, k [T, ld] hold H / group heads of dk from their offsets (head h reads head
     h // group), v holds H heads of dv. Either ``decay`` [H] (a constant, b = 1) or ``dt`` [T, ld] with
     ``dt_bias`` and ``a_log`` [H] (dt' = softplus(dt + bias), a = exp(-exp(a_log) dt'), b = dt').
-    ``activate``: SiLU on q, k, v as they are read. All 32-bit."""
+    ``activate``: SiLU on q, k, v as they are read. All 32-bit.
+    ``part_len`` > 0 cuts segments into parts of that many tokens which run side by side (three launches: the
+    parts from zero states, the parts' start states, what the start states add); it needs ``ws_state``
+    [scan_parts(T, R, part_len), H * dk * dv] and ``ws_decay`` [T, H]. Results differ from the one-launch form by
+    rounding only."""
     T = out.shape[0]
     if out.shape != (T, num_heads * dv):
         raise KernelError("linear_scan: out must be [T, H*dv]")
@@ -308,6 +313,12 @@ def linear_scan(q: torch.Tensor, q_offset: int, k: torch.Tensor, k_offset: int, 
     if state.dim() != 2 or state_offset < 0 or state_offset + num_heads * dk * dv > state.shape[1]:
         raise KernelError("linear_scan: the state does not fit the slot")
     R = seg_start.numel()
+    max_parts = 0
+    if part_len:
+        max_parts = (T + part_len - 1) // part_len          # no segment is longer than the step
+        if ws_state is None or ws_decay is None or ws_state.numel() < scan_parts(T, R, part_len) * num_heads * dk * dv or \
+                ws_decay.numel() < T * num_heads:
+            raise KernelError("linear_scan: the workspaces of the parts are missing or too small")
     check(lib().gi_linear_scan(
         _dev(q, "q", torch.float32), q.shape[1], int(q_offset), _dev(k, "k", torch.float32), k.shape[1], int(k_offset),
         _dev(v, "v", torch.float32), v.shape[1], int(v_offset), num_heads, group, dk, dv, int(bool(activate)),
@@ -315,7 +326,18 @@ def linear_scan(q: torch.Tensor, q_offset: int, k: torch.Tensor, k_offset: int, 
         _opt(dt_bias, "dt_bias", torch.float32), _opt(a_log, "a_log", torch.float32), _opt(skip, "skip", torch.float32),
         _dev(state, "state", torch.float32), state.shape[1], int(state_offset), _dev(seg_start, "seg_start", torch.int32),
         _dev(seg_len, "seg_len", torch.int32), _dev(state_slots, "state_slots", torch.int32), _dev(out, "out", torch.float32),
-        R, _stream()), "linear_scan")
+        R, int(part_len), max_parts, _opt(ws_state, "ws_state", torch.float32), _opt(ws_decay, "ws_decay", torch.float32),
+        _stream()), "linear_scan")
+    if part_len:
+        count_launches(2)
+
+
+SCAN_PART = 128          # tokens per part of a long segment (see linear_scan)
+
+
+def scan_parts(T: int, R: int, part_len: int = SCAN_PART) -> int:
+    """An upper bound of the parts that R segments of T tokens together make."""
+    return T // part_len + R
 
 
 def gated_group_norm(y: torch.Tensor, gate: torch.Tensor, gate_offset: int, weight: torch.Tensor, out: torch.Tensor,

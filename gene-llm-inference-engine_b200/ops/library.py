@@ -38,7 +38,7 @@ _SIGNATURES = {
                        c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "gi_linear_scan": [c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                        c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_longlong,
-                       c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
+                       c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p],
     "gi_gated_group_norm": [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float,
                             c_int, c_float, c_void_p],
     "gi_gemm_simt": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,

@@ -15,6 +15,19 @@ from ..ops.linear import Linear
 from .registry import register_mixer
 
 
+def _scan_workspaces(ctx, T: int, H: int, dk: int, dv: int):
+    """(part_len, ws_state, ws_decay) for a step's recurrence: segments that fit one part run in one launch on the
+    state slot itself; longer ones are cut into parts that run side by side (kernels.linear_scan)."""
+    if T <= kernels.SCAN_PART:
+        return {}
+    R = ctx.n_requests
+    parts = kernels.scan_parts(T, R)
+    most = getattr(ctx, "max_step_tokens", T) // kernels.SCAN_PART + ctx.max_requests
+    ws_state = ctx.scratch("scan_part_states", (parts, H * dk * dv), torch.float32, capacity=max(parts, most))
+    ws_decay = ctx.scratch("scan_decays", (T, H), torch.float32)
+    return {"part_len": kernels.SCAN_PART, "ws_state": ws_state, "ws_decay": ws_decay}
+
+
 def _vector(weights, name: str, n: int, build, what: str) -> torch.Tensor:
     w = weights[name]
     if w.numel() != n or w.dim() != 1:
@@ -78,7 +91,8 @@ class LinearAttentionMixer:
         self.w_in.forward(xn, proj)
         o = ctx.scratch("lin_att_out", (T, H * dv), torch.float32)
         kernels.linear_scan(proj, 0, proj, H * dk, proj, 2 * H * dk, H, 1, dk, dv, self.activate,
-                            ctx.state(run.cache_layer), 0, ctx.seg_start, ctx.seg_len, ctx.state_slots, o, decay=self.decay)
+                            ctx.state(run.cache_layer), 0, ctx.seg_start, ctx.seg_len, ctx.state_slots, o, decay=self.decay,
+                            **_scan_workspaces(ctx, T, H, dk, dv))
         y = ctx.scratch("lin_att_normed", (T, H * dv), self.dtype)
         kernels.gated_group_norm(o, proj, 2 * H * dk + H * dv, self.norm, y, 1, self.eps, gate_first=False,
                                  out_scale=self.out_scale)
@@ -161,7 +175,7 @@ class StateSpaceMixer:
         # q = C, k = B, v = x; a and b from the step size
         kernels.linear_scan(xbc, inner + G * N, xbc, inner, xbc, 0, H, H // G, N, P, False, state, 0, ctx.seg_start,
                             ctx.seg_len, ctx.state_slots, y, dt=proj, dt_offset=inner + C, dt_bias=self.dt_bias,
-                            a_log=self.a_log, skip=self.skip)
+                            a_log=self.a_log, skip=self.skip, **_scan_workspaces(ctx, T, H, N, P))
         yn = ctx.scratch("ssm_normed", (T, inner), self.dtype)
         kernels.gated_group_norm(y, proj, 0, self.norm, yn, self.norm_groups, self.eps, gate_first=True,
                                  out_scale=self.out_scale)

@@ -234,6 +234,38 @@ def test_state_space_mixer_with_state_and_convolution_inputs_carried_across_step
             _close(got[r], want[r], dtype, f"state space, request {r}, {len(cuts)} steps")
 
 
+@pytest.mark.parametrize("kind", ["linear_attention", "state_space"])
+def test_long_portions_are_cut_into_parts_that_run_side_by_side(kind):
+    """Steps of more than 128 tokens cut every segment into parts of 128 (zero-state scans, linked start states,
+    the start states' share added): the same results as token by token, parts ending inside and at the end of
+    segments, beside single tokens, from states that earlier steps left."""
+    from geneinfer_b200.parts import MIXERS
+    D, dtype = 40, torch.float32
+    g = torch.Generator().manual_seed(21)
+    if kind == "linear_attention":
+        m = {"heads": 2, "dim": 32, "vdim": 48, "decay": [1.0, 0.93]}
+        w = _lin_weights(D, m, g)
+        part = MIXERS[kind]({"hidden_size": D, "num_heads": 2, "key_dim": 32, "value_dim": 48, "decay": m["decay"], "norm_eps": 1e-5},
+                            {"w_in": torch.cat([w["p.q"], w["p.k"], w["p.v"], w["p.g"]]), "w_o": w["p.o"], "norm": w["p.norm"]},
+                            _build(dtype))
+        plain = lambda x: pn.lightning_mixer(x, w, "p.", m, 1e-5)
+    else:
+        m = dict(SSM, heads=2, groups=1, state=24)
+        w = _ssm_weights(D, m, g)
+        part = MIXERS[kind]({"hidden_size": D, "num_heads": 2, "head_dim": 24, "state_size": 24, "groups": 1, "conv_taps": 4,
+                             "norm_groups": 2, "norm_eps": 1e-5},
+                            {"w_in": w["p.in"], "w_o": w["p.o"], "conv": w["p.conv"], "conv_bias": w["p.conv.b"],
+                             "dt_bias": w["p.dt_bias"], "a_log": w["p.A_log"], "skip": w["p.D"], "norm": w["p.norm"]}, _build(dtype))
+        plain = lambda x: pn.right_mixer(x, w, "p.", m, 1e-5) @ w["p.o"].T
+    inputs = [_bf(0.5 * torch.randn(n, D, generator=g)) for n in (300, 2, 259)]
+    want = [plain(x) for x in inputs]
+    for cuts in ([[300, 2, 259]], [[129, 1, 3], [43, 1, 128], [128, 0, 128]]):
+        ctx = MiniCtx(dtype, 3, state_floats=part.state_need().shape[0], max_len=320)
+        got = _run_mixer(part, ctx, inputs, cuts, dtype, D)
+        for r in range(3):
+            _close(got[r], want[r], dtype, f"{kind} in parts, request {r}, {len(cuts)} steps")
+
+
 ATT = {"heads": 6, "kv_heads": 2, "dim": 32, "vdim": 32, "mask": {"size": 11}, "rot": {"base": 300.0, "dims": 16}, "scale": 0.4}
 
 
