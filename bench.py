@@ -474,7 +474,7 @@ def nipadra_kernel_table(width, heads, kv_heads, head_dim, window, T, pk):
             proj, 0, proj, D, proj, 2 * D, H, 1, 128, 128, True, state, 0, s0, sl, slots, out, decay=decay, **parts), scan_bytes,
             simt=rows_n * H * 128 * 128 * (4.0 if parts else 3.0))
         y = torch.empty(rows_n, D, dtype=torch.bfloat16, device=dev)
-        add(f"gated_group_norm ({what})", "swiglu", lambda: K.gated_group_norm(out, proj, 3 * D, w, y, 1, 1e-6, False), rows_n * D * 10)
+        add(f"gated_group_norm ({what})", "rmsnorm", lambda: K.gated_group_norm(out, proj, 3 * D, w, y, 1, 1e-6, False), rows_n * D * 10)
         # state space: heads of 64, state 128
         Hs, N = D // 64, 128
         C = D + 2 * N

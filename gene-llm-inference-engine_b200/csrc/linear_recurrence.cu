@@ -361,7 +361,10 @@ scan_apply_kernel(const ScanArgs p) {
 
 // ---------------------------------------------------------------------------------- gated group norm
 // One block per (token, group). mode 0: out = w * unit_rms(y) * sigmoid(gate); mode 1: out = w * unit_rms(y * silu(gate)).
-template <typename TOut>
+// Groups of at most 4096 channels in 16-byte pieces (kVec) are read once and kept in registers between the sum
+// and the scaling; the sum's order (a fixed strided assignment, a fixed xor tree, the warps in index order) is
+// the same in both forms.
+template <typename TOut, bool kVec>
 __global__ void __launch_bounds__(256)
 gated_group_norm_kernel(const float* __restrict__ y, const float* __restrict__ gate, int ld_gate, int gate_off,
                         const float* __restrict__ weight, TOut* __restrict__ out, int W, int groups, float eps,
@@ -372,25 +375,60 @@ gated_group_norm_kernel(const float* __restrict__ y, const float* __restrict__ g
     const int n = W / groups;
     const float* yr = y + static_cast<size_t>(t) * W + grp * n;
     const float* gr = gate + static_cast<size_t>(t) * ld_gate + gate_off + grp * n;
+    TOut* o = out + static_cast<size_t>(t) * W + grp * n;
+    const float* w = weight + grp * n;
     float ss = 0.f;
-    for (int d = threadIdx.x; d < n; d += 256) {
-        const float v = mode == 1 ? yr[d] * silu_f(gr[d]) : yr[d];
-        ss = fmaf(v, v, ss);
+    float4 kept[4], gk[4];
+    if (kVec) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int i = threadIdx.x + k * 256;
+            kept[k] = gk[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (i < n / 4) {
+                kept[k] = reinterpret_cast<const float4*>(yr)[i];
+                gk[k] = reinterpret_cast<const float4*>(gr)[i];
+                if (mode == 1) {
+                    kept[k].x *= silu_f(gk[k].x); kept[k].y *= silu_f(gk[k].y);
+                    kept[k].z *= silu_f(gk[k].z); kept[k].w *= silu_f(gk[k].w);
+                }
+            }
+            ss = fmaf(kept[k].x, kept[k].x, ss); ss = fmaf(kept[k].y, kept[k].y, ss);
+            ss = fmaf(kept[k].z, kept[k].z, ss); ss = fmaf(kept[k].w, kept[k].w, ss);
+        }
+    } else {
+        for (int d = threadIdx.x; d < n; d += 256) {
+            const float v = mode == 1 ? yr[d] * silu_f(gr[d]) : yr[d];
+            ss = fmaf(v, v, ss);
+        }
     }
     ss = warp_sum(ss);
     if ((threadIdx.x & 31) == 0) warp_part[threadIdx.x >> 5] = ss;
     __syncthreads();
     float total = 0.f;
 #pragma unroll
-    for (int w = 0; w < 8; ++w) total += warp_part[w];
+    for (int k = 0; k < 8; ++k) total += warp_part[k];
     const float scale = 1.0f / sqrtf(total / static_cast<float>(n) + eps);
-    TOut* o = out + static_cast<size_t>(t) * W + grp * n;
-    const float* w = weight + grp * n;
-    for (int d = threadIdx.x; d < n; d += 256) {
-        float v;
-        if (mode == 1) v = w[d] * (scale * (yr[d] * silu_f(gr[d])));
-        else v = w[d] * (scale * yr[d]) * (1.0f / (1.0f + expf(-gr[d])));
-        o[d] = from_float<TOut>(v * out_scale);
+    if (kVec) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int i = threadIdx.x + k * 256;
+            if (i >= n / 4) continue;
+            const float4 ww = reinterpret_cast<const float4*>(w)[i];
+            float r[4] = {ww.x * (scale * kept[k].x), ww.y * (scale * kept[k].y), ww.z * (scale * kept[k].z), ww.w * (scale * kept[k].w)};
+            if (mode == 0) {
+                r[0] *= 1.0f / (1.0f + expf(-gk[k].x)); r[1] *= 1.0f / (1.0f + expf(-gk[k].y));
+                r[2] *= 1.0f / (1.0f + expf(-gk[k].z)); r[3] *= 1.0f / (1.0f + expf(-gk[k].w));
+            }
+#pragma unroll
+            for (int c = 0; c < 4; ++c) o[4 * i + c] = from_float<TOut>(r[c] * out_scale);
+        }
+    } else {
+        for (int d = threadIdx.x; d < n; d += 256) {
+            float v;
+            if (mode == 1) v = w[d] * (scale * (yr[d] * silu_f(gr[d])));
+            else v = w[d] * (scale * yr[d]) * (1.0f / (1.0f + expf(-gr[d])));
+            o[d] = from_float<TOut>(v * out_scale);
+        }
     }
 }
 
@@ -470,12 +508,17 @@ static int gi_gated_group_norm_impl(const float* y, const float* gate, int ld_ga
     GI_REQUIRE(mode == 0 || mode == 1, "gated_group_norm: unknown mode %d", mode);
     GI_REQUIRE(gate_off >= 0 && gate_off + W <= ld_gate, "gated_group_norm: the gate lies outside its row of %d", ld_gate);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (out_dtype == kBF16)
-        launch_kernel((gated_group_norm_kernel<__nv_bfloat16>), dim3(T, groups), dim3(256), 0, st, y, gate, ld_gate, gate_off, weight,
-                      static_cast<__nv_bfloat16*>(out), W, groups, eps, mode, out_scale);
-    else if (out_dtype == kF32)
-        launch_kernel((gated_group_norm_kernel<float>), dim3(T, groups), dim3(256), 0, st, y, gate, ld_gate, gate_off, weight,
-                      static_cast<float*>(out), W, groups, eps, mode, out_scale);
+    const int n = W / groups;
+    const bool vec = n % 4 == 0 && n <= 4096 && W % 4 == 0 && ld_gate % 4 == 0 && gate_off % 4 == 0 &&
+                     reinterpret_cast<uintptr_t>(y) % 16 == 0 && reinterpret_cast<uintptr_t>(gate) % 16 == 0 &&
+                     reinterpret_cast<uintptr_t>(weight) % 16 == 0;
+    if (out_dtype == kBF16) {
+        if (vec) launch_kernel((gated_group_norm_kernel<__nv_bfloat16, true>), dim3(T, groups), dim3(256), 0, st, y, gate, ld_gate, gate_off, weight, static_cast<__nv_bfloat16*>(out), W, groups, eps, mode, out_scale);
+        else launch_kernel((gated_group_norm_kernel<__nv_bfloat16, false>), dim3(T, groups), dim3(256), 0, st, y, gate, ld_gate, gate_off, weight, static_cast<__nv_bfloat16*>(out), W, groups, eps, mode, out_scale);
+    } else if (out_dtype == kF32) {
+        if (vec) launch_kernel((gated_group_norm_kernel<float, true>), dim3(T, groups), dim3(256), 0, st, y, gate, ld_gate, gate_off, weight, static_cast<float*>(out), W, groups, eps, mode, out_scale);
+        else launch_kernel((gated_group_norm_kernel<float, false>), dim3(T, groups), dim3(256), 0, st, y, gate, ld_gate, gate_off, weight, static_cast<float*>(out), W, groups, eps, mode, out_scale);
+    }
     else
         GI_REQUIRE(false, "gated_group_norm: unsupported output dtype code %d", out_dtype);
     return check_launch("gated_group_norm");

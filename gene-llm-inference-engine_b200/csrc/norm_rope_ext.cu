@@ -78,10 +78,39 @@ gated_act_kernel(const float* __restrict__ gu, TOut* __restrict__ out, int I, si
     out[i] = from_float<TOut>(act_apply(gu[t * 2 * I + c], act) * gu[t * 2 * I + I + c]);
 }
 
+// The same, four channels to a thread with 16-byte accesses (I a multiple of 4, pointers aligned).
+template <typename TOut>
+__global__ void __launch_bounds__(256)
+gated_act4_kernel(const float* __restrict__ gu, TOut* __restrict__ out, int I4, size_t total4, int act) {
+    pdl_prologue();
+    const size_t i = static_cast<size_t>(blockIdx.x) * 256 + threadIdx.x;
+    if (i >= total4) return;
+    const size_t t = i / I4;
+    const int c = static_cast<int>(i % I4);
+    const float4* row = reinterpret_cast<const float4*>(gu) + t * 2 * I4;
+    const float4 g = row[c], u = row[I4 + c];
+    const float r0 = act_apply(g.x, act) * u.x, r1 = act_apply(g.y, act) * u.y, r2 = act_apply(g.z, act) * u.z,
+                r3 = act_apply(g.w, act) * u.w;
+    if constexpr (sizeof(TOut) == 4) {
+        *reinterpret_cast<float4*>(out + 4 * i) = make_float4(r0, r1, r2, r3);
+    } else {
+        const __nv_bfloat162 lo = __floats2bfloat162_rn(r0, r1), hi = __floats2bfloat162_rn(r2, r3);
+        uint2 raw;
+        raw.x = *reinterpret_cast<const uint32_t*>(&lo);
+        raw.y = *reinterpret_cast<const uint32_t*>(&hi);
+        *reinterpret_cast<uint2*>(out + 4 * i) = raw;
+    }
+}
+
 constexpr int kNrsWarps = 4;
 constexpr int kNrsMaxHead = 256;
 
-// One block per token, a warp per head (query heads first, then key heads).
+// A warp per head (query heads first, then key heads), a lane per pair of dimensions: both members of a rotation
+// pair are the lane's own, the head's sum of squares is one warp reduction, nothing goes through shared memory but
+// the token's sines and cosines, which all heads of the block share. Many rows: a block per token; few rows (decoding):
+// a block per token and four heads. Head sizes up to 256 (four pairs a lane), even.
+constexpr int kNrsPairs = kNrsMaxHead / 64;
+
 template <typename T>
 __global__ void __launch_bounds__(kNrsWarps * 32)
 norm_rope_store_kernel(const float* __restrict__ in, int ld, int q_off, int k_off, int v_off,
@@ -92,10 +121,13 @@ norm_rope_store_kernel(const float* __restrict__ in, int ld, int q_off, int k_of
                        T* __restrict__ q_out, T* __restrict__ k_cache, T* __restrict__ v_cache,
                        int H, int Hkv, int hd, int page_size, int write_kv) {
     pdl_prologue();
-    __shared__ float s_head[kNrsWarps][kNrsMaxHead];
+    __shared__ float s_cos[kNrsMaxHead / 2], s_sin[kNrsMaxHead / 2];
     const int t = blockIdx.x;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int pos = positions[t];
+    const int half = freq ? rot_half : 0;
+    for (int i = threadIdx.x; i < half; i += kNrsWarps * 32) sincosf(static_cast<float>(pos) * freq[i], &s_sin[i], &s_cos[i]);
+    __syncthreads();
     const float* row = in + static_cast<size_t>(t) * ld;
     size_t kv_base = 0;
     if (write_kv) {
@@ -103,42 +135,62 @@ norm_rope_store_kernel(const float* __restrict__ in, int ld, int q_off, int k_of
         kv_base = (static_cast<size_t>(page) * Hkv * page_size + (pos % page_size)) * hd;
     }
     const int n_heads = H + (write_kv ? Hkv : 0);
-    float* sh = s_head[warp];
-    for (int head = warp; head < n_heads; head += kNrsWarps) {
+    const int n_pairs = hd / 2;
+    for (int head = blockIdx.y * kNrsWarps + warp; head < n_heads; head += kNrsWarps * gridDim.y) {
         const bool is_q = head < H;
         const float* src = row + (is_q ? q_off + head * hd : k_off + (head - H) * hd);
         const float* nw = is_q ? q_norm : k_norm;
+        float va[kNrsPairs], vb[kNrsPairs];
+        int ia[kNrsPairs], ib[kNrsPairs];
         float ss = 0.f;
-        for (int d = lane; d < hd; d += 32) {
-            const float v = src[d];
-            sh[d] = v;
-            ss = fmaf(v, v, ss);
-        }
-        ss = warp_sum(ss);
-        __syncwarp();
-        if (nw) {
-            const float scale = 1.0f / sqrtf(ss / static_cast<float>(hd) + eps);
-            for (int d = lane; d < hd; d += 32) sh[d] = nw[d] * (scale * sh[d]);
-            __syncwarp();
+#pragma unroll
+        for (int u = 0; u < kNrsPairs; ++u) {
+            const int pr = lane + 32 * u;
+            // pair pr: a rotation pair while pr < half, else two neighbouring dimensions behind the rotated ones
+            if (interleaved || pr >= half) {
+                const int base = interleaved ? 2 * pr : 2 * half + 2 * (pr - half);
+                ia[u] = base; ib[u] = base + 1;
+            } else {
+                ia[u] = pr; ib[u] = pr + half;
+            }
+            const bool in_head = pr < n_pairs;
+            va[u] = in_head ? src[ia[u]] : 0.f;
+            vb[u] = in_head ? src[ib[u]] : 0.f;
+            ss = fmaf(va[u], va[u], ss);
+            ss = fmaf(vb[u], vb[u], ss);
         }
         T* dst = is_q ? q_out + (static_cast<size_t>(t) * H + head) * hd
                       : k_cache + kv_base + static_cast<size_t>(head - H) * page_size * hd;
-        const int half = freq ? rot_half : 0;
-        for (int i = lane; i < half; i += 32) {
-            const int ia = interleaved ? 2 * i : i, ib = interleaved ? 2 * i + 1 : i + half;
-            float sn, cs;
-            sincosf(static_cast<float>(pos) * freq[i], &sn, &cs);
-            const float a = sh[ia], b = sh[ib];
-            dst[ia] = from_float<T>(a * cs - b * sn);
-            dst[ib] = from_float<T>(b * cs + a * sn);
-        }
-        for (int d = 2 * half + lane; d < hd; d += 32) dst[d] = from_float<T>(sh[d]);
         if (!is_q) {
+            // the values: copied from their columns as they are (the keys themselves where the design says so)
             const float* vsrc = row + v_off + (head - H) * hd;
             T* vdst = v_cache + kv_base + static_cast<size_t>(head - H) * page_size * hd;
             for (int d = lane; d < hd; d += 32) vdst[d] = from_float<T>(vsrc[d]);
         }
-        __syncwarp();
+        if (nw) {
+            ss = warp_sum(ss);
+            const float scale = 1.0f / sqrtf(ss / static_cast<float>(hd) + eps);
+#pragma unroll
+            for (int u = 0; u < kNrsPairs; ++u) {
+                if (lane + 32 * u < n_pairs) {
+                    va[u] = nw[ia[u]] * (scale * va[u]);
+                    vb[u] = nw[ib[u]] * (scale * vb[u]);
+                }
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < kNrsPairs; ++u) {
+            const int pr = lane + 32 * u;
+            if (pr >= n_pairs) continue;
+            float a = va[u], b = vb[u];
+            if (pr < half) {
+                const float sn = s_sin[pr], cs = s_cos[pr];
+                const float ra = a * cs - b * sn, rb = b * cs + a * sn;
+                a = ra; b = rb;
+            }
+            dst[ia[u]] = from_float<T>(a);
+            dst[ib[u]] = from_float<T>(b);
+        }
     }
 }
 
@@ -179,6 +231,15 @@ static int gi_gated_act_impl(const float* gate_up, void* out, int out_dtype, int
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const size_t total = static_cast<size_t>(T) * I;
     const unsigned blocks = static_cast<unsigned>((total + 255) / 256);
+    if (I % 4 == 0 && reinterpret_cast<uintptr_t>(gate_up) % 16 == 0 && reinterpret_cast<uintptr_t>(out) % 16 == 0 &&
+        (out_dtype == kBF16 || out_dtype == kF32)) {
+        const unsigned blocks4 = static_cast<unsigned>((total / 4 + 255) / 256);
+        if (out_dtype == kBF16)
+            launch_kernel((gated_act4_kernel<__nv_bfloat16>), dim3(blocks4), dim3(256), 0, st, gate_up, static_cast<__nv_bfloat16*>(out), I / 4, total / 4, act);
+        else
+            launch_kernel((gated_act4_kernel<float>), dim3(blocks4), dim3(256), 0, st, gate_up, static_cast<float*>(out), I / 4, total / 4, act);
+        return check_launch("gated_act");
+    }
     if (out_dtype == kBF16)
         launch_kernel((gated_act_kernel<__nv_bfloat16>), dim3(blocks), dim3(256), 0, st, gate_up, static_cast<__nv_bfloat16*>(out), I, total, act);
     else if (out_dtype == kF32)
@@ -195,18 +256,21 @@ static int gi_norm_rope_store_impl(const float* in, int ld, int q_off, int k_off
                                    int page_size, int write_kv, void* stream) {
     if (T == 0) return 0;
     GI_REQUIRE(T > 0 && H > 0 && Hkv > 0 && hd > 0 && page_size > 0, "norm_rope_store: sizes must be positive");
-    GI_REQUIRE(hd <= kNrsMaxHead, "norm_rope_store: head size %d exceeds %d", hd, kNrsMaxHead);
+    GI_REQUIRE(hd <= kNrsMaxHead && hd % 2 == 0, "norm_rope_store: head size %d is odd or exceeds %d", hd, kNrsMaxHead);
     GI_REQUIRE(2 * rot_half <= hd, "norm_rope_store: rotary size %d exceeds the head size %d", 2 * rot_half, hd);
     GI_REQUIRE(q_off >= 0 && k_off >= 0 && v_off >= 0 && q_off + H * hd <= ld && k_off + Hkv * hd <= ld && v_off + Hkv * hd <= ld,
                "norm_rope_store: the columns of queries, keys or values lie outside the input row of %d", ld);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    GI_REQUIRE(T <= 2147483647, "norm_rope_store: too many rows");
+    // few rows (decoding): the heads of a token are spread over blocks; many rows: a block per token
+    const unsigned head_blocks = T >= 256 ? 1u : static_cast<unsigned>(std::min((H + Hkv + kNrsWarps - 1) / kNrsWarps, 65535));
     if (dtype == kF32)
-        launch_kernel((norm_rope_store_kernel<float>), dim3(T), dim3(kNrsWarps * 32), 0, st, in, ld, q_off, k_off, v_off, q_norm,
+        launch_kernel((norm_rope_store_kernel<float>), dim3(T, head_blocks), dim3(kNrsWarps * 32), 0, st, in, ld, q_off, k_off, v_off, q_norm,
                       k_norm, eps, freq, rot_half, interleaved, positions, row_req, block_tables, table_stride,
                       static_cast<float*>(q_out), static_cast<float*>(k_cache), static_cast<float*>(v_cache), H, Hkv, hd,
                       page_size, write_kv);
     else if (dtype == kBF16)
-        launch_kernel((norm_rope_store_kernel<__nv_bfloat16>), dim3(T), dim3(kNrsWarps * 32), 0, st, in, ld, q_off, k_off, v_off,
+        launch_kernel((norm_rope_store_kernel<__nv_bfloat16>), dim3(T, head_blocks), dim3(kNrsWarps * 32), 0, st, in, ld, q_off, k_off, v_off,
                       q_norm, k_norm, eps, freq, rot_half, interleaved, positions, row_req, block_tables, table_stride,
                       static_cast<__nv_bfloat16*>(q_out), static_cast<__nv_bfloat16*>(k_cache),
                       static_cast<__nv_bfloat16*>(v_cache), H, Hkv, hd, page_size, write_kv);
