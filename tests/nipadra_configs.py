@@ -55,6 +55,19 @@ NIP_Q = {
     ],
 }
 
+# L: linear attention only (a model that keeps no pages at all); A: the parallel pair only, each layer its own window
+NIP_L = {
+    "architecture": "Nipadra", "width": 64, "vocab": 150, "norm": {"eps": 1e-6}, "postln_alpha": 1.0,
+    "layers": [lightning(2, 32, 32, [0.9, 0.99], ff=96), lightning(4, 16, 16, [0.5, 0.8, 0.95, 1.0])],
+}
+NIP_A = {
+    "architecture": "Nipadra", "width": 80, "vocab": 170, "norm": {"eps": 1e-5}, "postln_alpha": 3.0,
+    "layers": [
+        parallel(attention(5, 5, 16, 33, 8, 1000.0, 0.25), state_space(5, 16, 16, 5, 2, 5), 1.0, 1.0),
+        parallel(attention(2, 1, 48, 5, 48, 20.0, 0.15), state_space(1, 80, 64, 1, 5, 1), 0.3, 0.9, ff=100),
+    ],
+}
+
 SHARP = {"std": 0.12}
 
 

@@ -446,6 +446,30 @@ def test_whole_prompts_decoding_portions_and_mixed_batches_agree_with_the_plain_
                 assert float(np.abs(row - ref).max()) < 2e-5 * max(1.0, float(np.abs(ref).max())), (name, key)
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["NIP_L", "NIP_A"])
+def test_models_of_one_kind_of_mixer(name, dtype, tmp_path):
+    """Linear attention only (no pages at all: the cache manager has no group) and the parallel pair only (one window
+    group per layer, a head size the tensor-core attention kernels are not built for)."""
+    config = getattr(nc, name)
+    folder = nc.make_model_dir(config, 29, str(tmp_path / name))
+    reqs = {f"r{i}": tc.random_tokens(n, config["vocab"], 700 + i) for i, n in enumerate([70, 1, 33, 140, 12])}
+    w, cfg = pn.load(folder)
+    exact = {rid: pn.forward(w, cfg, toks).numpy() for rid, toks in reqs.items()}
+    plain, tol = exact, 3e-5
+    if dtype == "bfloat16":
+        plain = {rid: pn.forward(w, cfg, toks, rnd=pn.bf16).numpy() for rid, toks in reqs.items()}
+        tol = 2.0 * max(tt.rel_err(plain[r], exact[r]) for r in reqs)
+    for steps in (tt.trace_whole(reqs), tt.trace_portions(reqs), tt.trace_mixed(reqs, seed=11, tail=10)):
+        engine = _engine(folder, dtype, n_pages=tt.max_tokens_of(steps, reqs, 16) // 16 + 4)
+        assert len(engine.cache.groups) == (0 if name == "NIP_L" else 2)
+        got = tt.run_in_process(engine, steps)
+        engine.check_status()
+        tt.compare(got, plain, tol, f"{name} {dtype}")
+        engine.cache.check_invariants()
+        assert engine.cache.slots.free_count == 4
+
+
 def test_long_decoding_past_the_window_and_over_page_borders(tmp_path_factory):
     """150 tokens decoded one by one after a 20-token prompt: the windows of 20 and 7 tokens pass over decoded
     tokens only, pages are given back behind the window, CUDA graphs replay the steps."""
