@@ -927,6 +927,7 @@ struct TcPersistentParams {
     int rows_p, rows_q, K;       // tokens, output columns of the accumulator tile space, reduction length
     int tiles_p, tiles_q;
     int up_row_offset;           // SwiGLU: row of the first up channel in the weight (= I)
+    int gate_act;                // SwiGLU epilogue: what is applied to the gate (0 SiLU, 1 ReLU, 2 tanh-GELU)
     int* status;
     int splits;                  // K is cut into this many ranges, each an accumulator tile of its own whose result is
     int kb_per_split;            //   stored split_rows rows further down in the output (a workspace; the ranges are
@@ -1240,8 +1241,17 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __gri
                             for (int e = 0; e < 4; ++e) {
                                 const float g0 = __uint_as_float(r[q4 * 8 + 2 * e]), g1 = __uint_as_float(r[q4 * 8 + 2 * e + 1]);
                                 const float u0 = __uint_as_float(u[q4 * 8 + 2 * e]), u1 = __uint_as_float(u[q4 * 8 + 2 * e + 1]);
-                                const float h0 = g0 * (1.0f / (1.0f + expf(-g0))) * u0;
-                                const float h1 = g1 * (1.0f / (1.0f + expf(-g1))) * u1;
+                                float h0, h1;
+                                if (p.gate_act == 0) {
+                                    h0 = g0 * (1.0f / (1.0f + expf(-g0))) * u0;
+                                    h1 = g1 * (1.0f / (1.0f + expf(-g1))) * u1;
+                                } else if (p.gate_act == 1) {
+                                    h0 = fmaxf(g0, 0.f) * u0;
+                                    h1 = fmaxf(g1, 0.f) * u1;
+                                } else {
+                                    h0 = 0.5f * g0 * (1.0f + tanhf(0.7978845608028654f * (g0 + 0.044715f * g0 * g0 * g0))) * u0;
+                                    h1 = 0.5f * g1 * (1.0f + tanhf(0.7978845608028654f * (g1 + 0.044715f * g1 * g1 * g1))) * u1;
+                                }
                                 __nv_bfloat162 hb = __floats2bfloat162_rn(h0, h1);
                                 packed[e] = *reinterpret_cast<uint32_t*>(&hb);
                             }
@@ -1691,7 +1701,8 @@ __global__ void reduce_splits_kernel(const float* __restrict__ ws, float* __rest
 }
 
 // Many tokens, one persistent CTA per SM. epilogue 0: C[M,N] = A W^T (32-bit); 1: C += A W^T (32-bit);
-// 2: W is [2N, K] = [gate; up] and C[M,N] = silu(A Wgate^T) * (A Wup^T) as bfloat16.
+// 2: W is [2N, K] = [gate; up] and C[M,N] = act(A Wgate^T) * (A Wup^T) as bfloat16, act named by the bits above the
+// epilogue's low byte (0 SiLU, 1 ReLU, 2 tanh-GELU).
 // block_q: 256 or 128 accumulator columns per tile.
 // splits > 1 (epilogues 0 and 1, N a multiple of 4, at most 8): K is cut into ranges whose tiles are work
 // items of their own; their results go to `workspace` (splits x ceil(M / 128) x 128 x N floats) and a
@@ -1704,7 +1715,10 @@ static int gi_gemm_tc_persistent_impl(const void* A, const void* W, void* C, int
     GI_REQUIRE(M > 0 && N > 0 && K > 0, "gemm_tc: sizes must be positive (M=%d, N=%d, K=%d)", M, N, K);
     GI_REQUIRE(K % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0,
                "gemm_tc: K=%d and the row strides (%lld, %lld) must be multiples of 8 (16-byte rows for TMA)", K, lda, ldw);
-    GI_REQUIRE(epilogue >= 0 && epilogue <= 2, "gemm_tc: unknown epilogue %d", epilogue);
+    const int gate_act = epilogue >> 8;
+    epilogue &= 0xff;
+    GI_REQUIRE(epilogue >= 0 && epilogue <= 2 && gate_act >= 0 && gate_act <= 2 && (gate_act == 0 || epilogue == kEpiSwiGLU),
+               "gemm_tc: unknown epilogue %d (activation %d)", epilogue, gate_act);
     const bool bf16_out = epilogue == kEpiSwiGLU;
     GI_REQUIRE((ldc * (bf16_out ? 2 : 4)) % 16 == 0, "gemm_tc: the output row stride %lld is not a multiple of 16 bytes", ldc);
     GI_REQUIRE((reinterpret_cast<uintptr_t>(A) % 16 == 0) && (reinterpret_cast<uintptr_t>(W) % 16 == 0) &&
@@ -1717,6 +1731,7 @@ static int gi_gemm_tc_persistent_impl(const void* A, const void* W, void* C, int
     p.tiles_p = pair ? (M + 2 * kBlockP - 1) / (2 * kBlockP) : (M + kBlockP - 1) / kBlockP;
     const int rows_per_tile_p = pair ? 2 * kBlockP : kBlockP;
     p.up_row_offset = N;
+    p.gate_act = gate_act;
     p.status = static_cast<int*>(status);
     const int total_kb = (K + kBlockK - 1) / kBlockK;
     p.splits = 1; p.kb_per_split = total_kb; p.split_rows = 0;

@@ -738,17 +738,19 @@ def gemm_swiglu_supported(M: int, I: int, K: int) -> bool:
     return M > 128 and K % 8 == 0 and I % 8 == 0
 
 
-def gemm_swiglu(a: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor) -> None:
-    """out[M, I] = silu(a @ w_gate^T) * (a @ w_up^T) as bfloat16, w_gate_up = [gate rows; up rows]
+def gemm_swiglu(a: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor, activation: str = "silu") -> None:
+    """out[M, I] = act(a @ w_gate^T) * (a @ w_up^T) as bfloat16, w_gate_up = [gate rows; up rows]
     [2I, K]: one tensor-core kernel whose epilogue applies the activation (the [M, 2I] intermediate
-    never exists in memory)."""
+    never exists in memory). ``activation``: one of ACTIVATIONS."""
+    if activation not in ACTIVATIONS:
+        raise KernelError(f"gemm_swiglu: unknown activation '{activation}'")
     M, K = a.shape
     I = out.shape[1]
     if w_gate_up.shape != (2 * I, K) or out.shape[0] != M:
         raise KernelError("gemm_swiglu: shapes do not agree")
     st = _tc_state(a.device)
     check(lib().gi_gemm_tc_persistent(_dev(a, "a", torch.bfloat16), _dev(w_gate_up, "w_gate_up", torch.bfloat16),
-                                      _dev(out, "out", torch.bfloat16), 2, M, I, K, K, K, I, 256,
+                                      _dev(out, "out", torch.bfloat16), 2 | (ACTIVATIONS[activation] << 8), M, I, K, K, K, I, 256,
                                       st.status.data_ptr(), 1, 0, 0, _paired(M, 256), _stream()), "gemm_swiglu")
 
 

@@ -46,9 +46,8 @@ class SwiGLUFeedForward:
     def forward(self, ctx, xn: torch.Tensor, x: torch.Tensor) -> None:
         T = xn.shape[0]
         h = ctx.scratch("ffn_hidden", (T, self.intermediate_size), self.dtype)
-        if self.activation == "silu" and self.dtype is torch.bfloat16 and \
-                kernels.gemm_swiglu_supported(T, self.intermediate_size, self.hidden_size):
-            kernels.gemm_swiglu(xn, self.w_gate_up.weight, h)      # activation in the product's epilogue
+        if self.dtype is torch.bfloat16 and kernels.gemm_swiglu_supported(T, self.intermediate_size, self.hidden_size):
+            kernels.gemm_swiglu(xn, self.w_gate_up.weight, h, self.activation)      # activation in the product's epilogue
         else:
             gu = ctx.scratch("gate_up", (T, 2 * self.intermediate_size), torch.float32)
             self.w_gate_up.forward(xn, gu)

@@ -146,8 +146,9 @@ def test_gated_activation(act):
     assert float((out.cpu() - want).abs().max()) < 1e-5
 
 
+@pytest.mark.parametrize("rows", [13, 200])          # 200 rows in bfloat16: the activation runs in the product's epilogue
 @pytest.mark.parametrize("dtype", DTYPES)
-def test_gated_feed_forward_part(dtype):
+def test_gated_feed_forward_part(dtype, rows):
     from geneinfer_b200.parts import FEED_FORWARDS
     D, I = 40, 112
     g = torch.Generator().manual_seed(4)
@@ -156,8 +157,8 @@ def test_gated_feed_forward_part(dtype):
     for act in ("relu", "gelu_tanh"):
         part = FEED_FORWARDS["gated_mlp"]({"hidden_size": D, "intermediate_size": I, "activation": act},
                                           {"w_gate_up": torch.cat([w["p.gate"], w["p.up"]]), "w_down": w["p.down"]}, _build(dtype))
-        xn = torch.randn(13, D, generator=g).to(dtype)
-        x = torch.randn(13, D, generator=g)
+        xn = torch.randn(rows, D, generator=g).to(dtype)
+        x = torch.randn(rows, D, generator=g)
         x_dev = x.clone().to(DEV)
         part.forward(MiniCtx(dtype, 1), xn.to(DEV), x_dev)
         rnd = pn.ident if dtype is torch.float32 else pn.bf16
