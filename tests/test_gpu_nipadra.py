@@ -524,6 +524,40 @@ def test_greedy_generation_through_the_engine_and_its_scheduler(dtype, tmp_path_
     assert engine.stats.max_running_seen == 3 and engine.steps.cache.slots.free_count == 3
 
 
+def test_a_preempted_request_is_recomputed_from_a_zeroed_state(tmp_path_factory):
+    """A pool too small for all requests: the scheduler preempts the youngest, whose state slot and pages go back;
+    it is recomputed later from its first token and must generate what it generates with room for all."""
+    from geneinfer_b200 import Engine
+    folder = _model_dir("q", tmp_path_factory)            # a window of 150: no page goes back while these requests run
+    prompts = [tc.random_tokens(n, 300, 300 + n) for n in (70, 64, 90)]
+    roomy = Engine(folder, dtype="float32", max_seq_len=256, max_running=3, kv_pages=64, step_tokens=48)
+    want = roomy.generate(prompts, max_new_tokens=40, temperature=0.0)
+    tight = Engine(folder, dtype="float32", max_seq_len=256, max_running=3, kv_pages=14, step_tokens=48)
+    got = tight.generate(prompts, max_new_tokens=40, temperature=0.0)
+    assert tight.stats.preemptions > 0, "the pool was meant to be too small: no request was preempted"
+    for a, b in zip(got, want):
+        assert sum(x != y for x, y in zip(a, b)) <= 1, (a, b)       # 32-bit: a near-tie at most
+    assert tight.steps.cache.slots.free_count == 3
+
+
+@pytest.mark.parametrize("page_size", [8, 12, 64])
+def test_other_page_sizes(page_size, tmp_path_factory):
+    """Pages of 8 and 64 positions (TMA-fed attention kernels) and of 12 (the general kernel also in bfloat16)."""
+    folder = _model_dir("q", tmp_path_factory)
+    reqs = {k: v for k, v in list(_requests("q").items())[:3]}
+    for dtype in ("float32", "bfloat16"):
+        plain, tol = _plain("q", folder, dtype), _tolerance("q", folder, dtype)
+        steps = tt.trace_mixed(reqs, seed=2, tail=20)
+        from geneinfer_b200.engine.loading import load_model
+        from geneinfer_b200.engine.step import StepEngine
+        model = load_model(folder, dtype=dtype, max_position=504)
+        engine = StepEngine(model, page_size=page_size, n_pages=tt.max_tokens_of(steps, reqs, 64) // page_size + 8, max_requests=4,
+                            max_step_tokens=512, debug_checks=True)
+        got = tt.run_in_process(engine, steps)
+        engine.check_status()
+        tt.compare(got, plain, tol, f"page size {page_size} {dtype}")
+
+
 def test_trace_replay_tool_and_command_line(tmp_path, tmp_path_factory):
     folder = _model_dir("p", tmp_path_factory)
     reqs = {k: v for k, v in list(_requests("p").items())[3:6]}
