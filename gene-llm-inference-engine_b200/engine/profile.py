@@ -27,6 +27,13 @@ OPERATIONS = {
     "gemm_simt": ("matrix products (32-bit)", 1),
     "gemm_swiglu": ("ffn gate+up with silu * up", 1),
     "swiglu": ("silu * up", None),
+    "scale_cast": ("residual scale + operand", None),
+    "residual_norm": ("norm after the residual sum", None),
+    "gated_act": ("act(gate) * up", None),
+    "norm_rope_store": ("q/k norm + rope + store", None),
+    "causal_conv": ("causal convolution", None),
+    "linear_scan": ("recurrence (state update + output)", None),
+    "gated_group_norm": ("gated norm", None),
     "copy_pages": ("page copies", None),
     "argmax": ("sampling", None),
     "sample": ("sampling", None),

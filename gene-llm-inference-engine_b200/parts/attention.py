@@ -22,8 +22,8 @@ class AttentionMixer:
 
     Options (each absent by default; any of them takes the mixer off the fused [q; k; v] product with
     rotation in its epilogue and onto the 32-bit projection followed by the norm+rotation+store kernel):
-    ``values`` = "keys": there is no value projection; the keys as projected, before norm and rotation, are
-    stored as the values (``w_qkv`` then has no value rows). ``qk_norm_eps``: queries and keys are
+    ``values`` = "keys": the model has no value projection; the value rows written to the pages are the key
+    projection's raw output, taken ahead of the per-head norm and the rotation (``w_qkv`` then has no value rows). ``qk_norm_eps``: queries and keys are
     normalised per head to unit RMS and multiplied by ``q_norm`` / ``k_norm`` [hd] (shared by the heads)
     before the rotation. ``sink``: the softmax's denominator has one more term, exp(0). ``head_gate``:
     ``w_qkv`` ends with H more rows, and head h's output is multiplied by the sigmoid of its row's product

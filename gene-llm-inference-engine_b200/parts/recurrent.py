@@ -1,6 +1,6 @@
 """Mixers that keep a state of fixed size per request instead of keys and values.
 
-Both run the same recurrence kernel, S_t = a_t S_(t-1) + b_t k_t v_t^T and o_t = S_t^T q_t (+ skip v_t), per
+Both run the same recurrence kernel, M_t = a_t M_(t-1) + b_t k_t (x) v_t and y_t = M_t^T q_t (+ skip v_t), per
 head over each request's rows in order, with the 32-bit state [H, dk, dv] in the request's state slot
 (``ctx.state(layer)[slot]``; the engine hands a new request a zeroed slot). They differ in where q, k, v, a and
 b come from and in the gated norm that follows.
@@ -37,14 +37,15 @@ def _vector(weights, name: str, n: int, build, what: str) -> torch.Tensor:
 
 @register_mixer("linear_attention")
 class LinearAttentionMixer:
-    """Linear attention with a constant decay per head: q, k [H, dk] and v [H, dv] are activated
-    projections of the input, S_t = decay_h S_(t-1) + k_t v_t^T, o_t = S_t^T q_t with no other scale; the
-    heads together are normalised to unit RMS (weight ``norm`` [H*dv]), multiplied by sigmoid(W_g input) and
-    projected by ``w_o``.
+    """Linear attention whose memory fades by a fixed factor per head. With u the input row, phi the activation and
+    lambda_h the head's factor:  q = phi(Wq u), k = phi(Wk u) (H heads of dk), v = phi(Wv u) (H heads of dv);
+    M_t = lambda_h M_(t-1) + k_t (x) v_t  (a dk x dv matrix per head, (x) the outer product);  y_t = M_t^T q_t, unscaled.
+    All heads' y side by side are brought to unit RMS as one vector, weighted by ``norm`` [H dv], gated elementwise
+    by sigmoid(Wg u) and sent through ``w_o``.
 
-    Params: ``hidden_size``, ``num_heads``, ``key_dim``, ``value_dim``, ``decay`` (one per head), ``norm_eps``,
+    Params: ``hidden_size``, ``num_heads``, ``key_dim``, ``value_dim``, ``decay`` (lambda, one per head), ``norm_eps``,
     ``activation`` ("silu" or "none") and optionally ``out_scale``. Weights: ``w_in`` [(2 H dk + 2 H dv), hidden]
-    (rows of q, k, v, then the gate), ``w_o`` [hidden, H dv], ``norm`` [H dv]."""
+    (rows of Wq, Wk, Wv, Wg in this order), ``w_o`` [hidden, H dv], ``norm`` [H dv]."""
 
     graph_safe = True
 
@@ -101,16 +102,18 @@ class LinearAttentionMixer:
 
 @register_mixer("state_space")
 class StateSpaceMixer:
-    """A selective state-space mixer in its scalar-decay (state-space duality) form. With inner = H P:
-    ``w_in`` maps the input to [z: inner | x: inner | B: G N | C: G N | dt: H]; x, B and C pass a causal
-    convolution per channel (``conv`` [channels, taps], the last column the current token's, bias
-    ``conv_bias``, zeros before the start) and SiLU; dt <- softplus(dt + ``dt_bias``) without a clamp; per head
-    (head h reads group h // (H / G)): S_t = exp(-exp(``a_log``_h) dt) S_(t-1) + dt B_t x_t^T (S is N x P),
-    y_t = S_t^T C_t + ``skip``_h x_t; then y * silu(z), unit RMS in ``norm_groups`` equal parts, times ``norm``,
-    and the projection ``w_o``. The request's state slot holds S and, behind it, the last taps-1 inputs of the
-    convolution [taps-1, channels].
+    """A selective state-space mixer whose decay is one number per head and token. ``w_in`` gives, per token, five
+    blocks in this order: a gate z (H P values), the signal u (H P), an input map B (G N), a read-out map C (G N) and a
+    raw step r (H). u, B and C go through a depthwise convolution over the last ``conv_taps`` tokens of the request
+    (``conv`` [channels, taps], column taps-1 weighs the newest token; ``conv_bias``; nothing before the first token)
+    followed by SiLU. With delta = softplus(r + ``dt_bias``) (no upper bound) and rho_h = exp(``a_log``_h), head h
+    (which shares B and C with the heads of its group, G groups of H / G heads) keeps an N x P matrix:
+    M_t = exp(-rho_h delta_t) M_(t-1) + delta_t B_t (x) u_t;  y_t = M_t^T C_t + ``skip``_h u_t.
+    y is gated by SiLU(z) first and only then brought to unit RMS, separately in each of ``norm_groups`` equal
+    slices, weighted by ``norm`` and sent through ``w_o``. A request's state slot holds M and, behind it, the
+    convolution's last taps-1 inputs [taps-1, channels].
 
-    Params: ``hidden_size``, ``num_heads``, ``head_dim`` (P), ``state_size`` (N), ``groups``, ``conv_taps``,
+    Params: ``hidden_size``, ``num_heads`` (H), ``head_dim`` (P), ``state_size`` (N), ``groups`` (G), ``conv_taps``,
     ``norm_groups``, ``norm_eps`` and optionally ``out_scale``."""
 
     graph_safe = True

@@ -64,8 +64,8 @@ def softplus(z):
 
 # ------------------------------------------------------------------------------------ lightning
 def lightning_mixer(h, w: Dict[str, torch.Tensor], p: str, m: dict, eps: float, dt=torch.float32, rnd=ident):
-    """q, k, v = silu of three projections; per head S_t = decay S_{t-1} + k_t v_t^T, o_t = S_t^T q_t;
-    the heads together are unit-normed, weighted, gated by sigmoid(W_g h) and projected."""
+    """Three activated projections feed a fading outer-product memory per head (S <- decay * S + k (x) v, read out
+    as S^T q); all heads' read-outs are normed as one vector, weighted, gated by a fourth projection's sigmoid."""
     T = h.shape[0]
     H, dk, dv = m["heads"], m["dim"], m["vdim"]
     hb = rnd(h)
@@ -99,8 +99,8 @@ def rotate_interleaved(v, positions, base: float, dims: int):
 
 
 def sink_window_attention(q, k, v, scale: float, window: int, rnd=ident):
-    """Softmax with one more in the denominator over the keys 0 <= i - j < window.
-    q [T, H, d]; k, v [T, G, d]."""
+    """Query i looks back over at most ``window`` keys, itself included; the weights' denominator carries an extra 1
+    (a phantom key of score 0 that contributes no value). q [T, H, d]; k, v [T, G, d]."""
     T, H, _ = q.shape
     G = k.shape[1]
     out = torch.zeros(T, H, v.shape[-1], dtype=q.dtype)
@@ -121,7 +121,7 @@ def left_mixer(h, w, p: str, m: dict, eps: float, dt=torch.float32, rnd=ident):
     hb = rnd(h)
     q = (hb @ w[p + "q"].to(dt).T).reshape(T, H, d)
     k = (hb @ w[p + "k"].to(dt).T).reshape(T, G, d)
-    v = rnd(k)                                             # the values are the keys as projected
+    v = rnd(k)                                             # values: the key projection's raw output
     q = norm_plain(q, w[p + "q.norm"], eps)
     kn = norm_plain(k, w[p + "k.norm"], eps)
     pos = range(T)
@@ -135,7 +135,8 @@ def left_mixer(h, w, p: str, m: dict, eps: float, dt=torch.float32, rnd=ident):
 
 # ------------------------------------------------------------------------------------ state-space side
 def causal_conv(u, weight, bias):
-    """u [T, C]; weight [C, taps], the last column is the current token's; zeros before the start."""
+    """Depthwise filter over time. u [T, C]; weight [C, taps] with column taps-1 on the newest token; the sequence is
+    padded with zeros on the left."""
     T, C = u.shape
     taps = weight.shape[1]
     pad = torch.cat([torch.zeros(taps - 1, C, dtype=u.dtype), u])

@@ -576,3 +576,9 @@ def test_trace_replay_tool_and_command_line(tmp_path, tmp_path_factory):
         assert t == int(np.argmax(logits)) or float(logits.max() - logits[t]) < 1e-4
         tokens.append(t)
     assert len(out) == 9
+    prof = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "gi_generate"), "--model", folder, "--prompt-ids", "5 9 2 100 7 7",
+                           "--steps", "9", "--temperature", "0", "--quiet", "--profile", "--max-seq-len", "64"],
+                          capture_output=True, text=True, timeout=600)
+    assert prof.returncode == 0, prof.stderr
+    for op in ("recurrence (state update + output)", "norm after the residual sum", "causal convolution", "attention", "gated norm"):
+        assert op in prof.stderr, f"--profile does not report '{op}':\n{prof.stderr}"
