@@ -1,6 +1,6 @@
 // Paged causal attention, general form: one block per (query row, query head), any mix of prompt
-// portions and single decoded tokens, any head size that is a multiple of 16 up to 256, any page
-// size, grouped key/value heads, optional sliding window.
+// portions and single decoded tokens, any head size up to 256 (rows of 16-byte pieces, head sizes that are
+// multiples of 8, are read so), any page size, grouped key/value heads, optional sliding window.
 //
 // Definition (src/model/transformer.cpp:228-255, src/kernels/kernels.cpp:87-104): for the query
 // at position P of its request, scores s_j = (q . k_j) * scale for j = lo..P only (causality is
@@ -23,6 +23,14 @@ constexpr int kMaxHeadDim = 256;
 
 template <typename T>
 __device__ __forceinline__ float dot_row(const float* __restrict__ q, const T* __restrict__ k, int hd);
+
+// The same chain of multiply-adds, element by element: head sizes whose rows are not 16-byte pieces.
+template <typename T>
+__device__ __forceinline__ float dot_row_scalar(const float* __restrict__ q, const T* __restrict__ k, int hd) {
+    float acc = 0.f;
+    for (int i = 0; i < hd; ++i) acc = fmaf(q[i], to_float(k[i]), acc);
+    return acc;
+}
 
 template <>
 __device__ __forceinline__ float dot_row<float>(const float* __restrict__ q, const float* __restrict__ k, int hd) {
@@ -96,7 +104,7 @@ paged_attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_
         if (valid) {
             const int page = table[j / page_size];
             row_off = ((static_cast<size_t>(page) * Hkv + g) * page_size + (j % page_size)) * hd;
-            score = dot_row<T>(s_q, k_cache + row_off, hd) * scale;
+            score = (hd % 8 == 0 ? dot_row<T>(s_q, k_cache + row_off, hd) : dot_row_scalar<T>(s_q, k_cache + row_off, hd)) * scale;
         }
         const float tile_max = warp_max(score);          // finite: a tile always holds a valid key
         const float m_new = fmaxf(m, tile_max);
@@ -155,7 +163,7 @@ paged_attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_
 using namespace gi;
 
 // 1 when the general kernel serves this head size: the model is refused when it is built, not at its first step.
-extern "C" int gi_attention_generic_supported(int hd) { return hd % 16 == 0 && hd >= 16 && hd <= kMaxHeadDim; }
+extern "C" int gi_attention_generic_supported(int hd) { return hd >= 1 && hd <= kMaxHeadDim; }
 
 static int gi_attention_generic_impl(const void* q, const void* k_cache, const void* v_cache, void* out, int dtype,
                                     const int* row_req, const int* positions, const int* block_tables,
@@ -165,8 +173,7 @@ static int gi_attention_generic_impl(const void* q, const void* k_cache, const v
     if (T == 0) return 0;
     GI_REQUIRE(T > 0 && H > 0 && Hkv > 0 && page_size > 0, "attention: sizes must be positive");
     GI_REQUIRE(H % Hkv == 0, "attention: %d query heads are not a multiple of %d key/value heads", H, Hkv);
-    GI_REQUIRE(hd % 16 == 0 && hd >= 16 && hd <= kMaxHeadDim,
-               "attention: head size %d is not supported (multiples of 16 up to %d)", hd, kMaxHeadDim);
+    GI_REQUIRE(hd >= 1 && hd <= kMaxHeadDim, "attention: head size %d is not supported (up to %d)", hd, kMaxHeadDim);
     GI_REQUIRE(T <= 65535, "attention: %d rows in one step exceed the grid limit 65535", T);
     dim3 grid(H, T);
     cudaStream_t st = static_cast<cudaStream_t>(stream);

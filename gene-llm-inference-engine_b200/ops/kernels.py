@@ -404,7 +404,7 @@ def attention_tma_pages(page_size: int) -> bool:
 
 
 def attention_supported(head_dim: int) -> bool:
-    """Whether any attention kernel of the library serves this head size (multiples of 16 up to 256)."""
+    """Whether any attention kernel of the library serves this head size (up to 256)."""
     return bool(lib().gi_attention_generic_supported(head_dim))
 
 

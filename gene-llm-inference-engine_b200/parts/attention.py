@@ -43,7 +43,7 @@ class AttentionMixer:
             raise ValueError("attention: num_heads must be a multiple of num_kv_heads")
         if not kernels.attention_supported(self.head_dim):
             raise ValueError(f"attention: head size {self.head_dim} is not supported by the attention kernels "
-                             f"(multiples of 16 up to 256)")
+                             f"(up to 256)")
         pos_spec = params.get("position") or PartSpec("none", {})
         self.position = build_part(POSITION_ENCODINGS, "position encoding", pos_spec, {}, build)
         self.values_are_keys = params.get("values", "projected") == "keys"

@@ -89,13 +89,32 @@ class _Ctx:
 
 def test_a_head_size_the_kernels_do_not_serve_is_refused_when_the_model_is_built(tmp_path):
     """config.json may give any even head size (the reference accepts it); the attention kernels serve
-    multiples of 16 up to 256. The refusal comes when the model is built, with the size in the message,
+    head sizes up to 256. The refusal comes when the model is built, with the size in the message,
     not at the first step after weights and pages are on the device."""
     from geneinfer_b200.engine.loading import load_model
-    config = dict(tc.TINY_A, head_dim=24, hidden_size=96, num_attention_heads=4, num_key_value_heads=2)
-    folder = tc.make_model_dir(config, tc.WEIGHTS_A, str(tmp_path / "hd24"))
-    with pytest.raises(ValueError, match="head size 24"):
+    config = dict(tc.TINY_A, head_dim=272, hidden_size=96, num_attention_heads=4, num_key_value_heads=2)
+    folder = tc.make_model_dir(config, tc.WEIGHTS_A, str(tmp_path / "hd272"))
+    with pytest.raises(ValueError, match="head size 272"):
         load_model(folder, dtype="float32")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_head_size_that_is_no_multiple_of_8_runs_on_the_general_kernel(dtype, tmp_path):
+    """Head size 24: rows of the cache are no 16-byte pieces; the general attention kernel reads them element by element."""
+    from geneinfer_b200.engine.loading import load_model
+    from geneinfer_b200.engine.step import StepEngine
+    config = dict(tc.TINY_A, head_dim=24, hidden_size=96, num_attention_heads=4, num_key_value_heads=2)
+    folder = tc.make_model_dir(config, tc.SHARP_A, str(tmp_path / "hd24"))
+    reqs = {"r0": tc.random_tokens(50, 256, 1), "r1": tc.random_tokens(21, 256, 2)}
+    w, cfg = pm.load_plain(folder)
+    exact = {rid: pm.plain_forward(w, cfg, toks).numpy() for rid, toks in reqs.items()}
+    plain, tol = exact, gf.TOL_F32
+    if dtype == "bfloat16":
+        plain = {rid: pm.plain_forward(pm.round_weights_bf16(w), cfg, toks, pm.bf16_rounding).numpy() for rid, toks in reqs.items()}
+        tol = 1.5 * max(tt.rel_err(plain[r], exact[r]) for r in reqs)
+    for steps in (tt.trace_whole(reqs), tt.trace_mixed(reqs, seed=3, tail=7)):
+        engine = StepEngine(load_model(folder, dtype=dtype), page_size=16, n_pages=12, max_requests=2, max_step_tokens=128)
+        tt.compare(tt.run_in_process(engine, steps), plain, tol, f"head size 24 {dtype}")
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
