@@ -268,9 +268,14 @@ def test_attention_window_edge(dtype, window):
 def test_attention_refuses_unsupported_head_size():
     from geneinfer_b200.ops import KernelError
     with pytest.raises(KernelError, match="head size"):
-        _attention_case("float32", 2, 1, 24, 16, [4], [4], None, 1)
-    with pytest.raises(KernelError, match="head size"):
         _attention_case("float32", 2, 1, 512, 16, [4], [4], None, 1)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("hd", [24, 20, 6])
+def test_attention_head_sizes_whose_rows_are_no_16_byte_pieces(dtype, hd):
+    got, want = _attention_case(dtype, 4, 2, hd, 16, ctx_lens=[40, 9], q_lens=[7, 9], window=None, seed=5)
+    close(got, want, dtype, f"head size {hd}", f32_tol=5e-6, bf16_tol=1e-2)
 
 
 @pytest.mark.parametrize("rows,V", [(1, 1), (3, 1000), (5, 128256), (2, 50257)])
