@@ -23,15 +23,36 @@ from .pages import OutOfPages, PagePool
 @dataclass(frozen=True)
 class CacheNeed:
     """What a mixer needs of the paged cache. ``window`` None keeps all keys; an integer w keeps
-    only the keys of the last w positions (a query at p reads positions p-w+1 .. p)."""
+    only the keys of the last w positions (a query at p reads positions p-w+1 .. p). ``chunk`` c: a query
+    reads only the keys of its own block of c positions counted from 0, so the pages of earlier blocks are
+    given back. ``value_dim``: the width of a value row when it is not ``head_dim``; 0 = no value pages (the
+    values are read out of the key rows)."""
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    value_dim: Optional[int] = None
+    chunk: Optional[int] = None
+
+    @property
+    def value_width(self) -> int:
+        return self.head_dim if self.value_dim is None else self.value_dim
 
     @property
     def group_key(self) -> Tuple:
-        return ("window", self.window, self.num_kv_heads, self.head_dim) if self.window else \
-               ("full", None, self.num_kv_heads, self.head_dim)
+        key = ("window", self.window, self.num_kv_heads, self.head_dim) if self.window else \
+              ("full", None, self.num_kv_heads, self.head_dim)
+        if self.chunk or self.value_width != self.head_dim:
+            key += (self.value_width, self.chunk)
+        return key
+
+    def first_needed(self, length: int) -> int:
+        """The lowest position that a query at position ``length`` or later still reads (0: everything)."""
+        first = 0
+        if self.window:
+            first = max(first, length - self.window + 1)
+        if self.chunk:
+            first = max(first, length // self.chunk * self.chunk)
+        return first
 
 
 @dataclass(frozen=True)
@@ -228,10 +249,9 @@ class CacheManager:
         rc.fresh_state = False
         ps = self.page_size
         for g, group in enumerate(self.groups):
-            w = group.need.window
-            if not w:
+            if not (group.need.window or group.need.chunk):
                 continue
-            first_needed = max(0, rc.length - w + 1)     # lowest position a query at >= length reads
+            first_needed = group.need.first_needed(rc.length)     # lowest position a query at >= length reads
             dead = first_needed // ps                    # pages wholly below it
             for i in range(rc.first_live[g], min(dead, rc.n_pages[g])):
                 if rc.tables[g][i] >= 0:
@@ -266,8 +286,7 @@ class CacheManager:
             raise RuntimeError("truncate: a request with per-request state cannot be rewound")
         ps = self.page_size
         for g, group in enumerate(self.groups):
-            w = group.need.window
-            if w and max(0, length - w + 1) // ps < rc.first_live[g]:
+            if group.need.first_needed(length) // ps < rc.first_live[g]:
                 raise RuntimeError(f"truncate: the window group has given back pages that position {length} would read")
         keep = (length + ps - 1) // ps
         for g, group in enumerate(self.groups):
@@ -284,7 +303,7 @@ class CacheManager:
         cache hit). The caller has retained each page for this request."""
         if rc.length != 0 or any(rc.n_pages):
             raise RuntimeError("adopt: the request is not empty")
-        if len(self.groups) != 1 or self.groups[0].need.window or self.state_layers:
+        if len(self.groups) != 1 or self.groups[0].need.window or self.groups[0].need.chunk or self.state_layers:
             raise RuntimeError("adopt: only models with one full-attention group and no state can share pages")
         for i, p in enumerate(pages):
             rc.tables[group][i] = p
@@ -298,7 +317,7 @@ class CacheManager:
         with Sequence::adopt and truncate for this, tools/multiseq_check_main.cpp:279-286). Neither
         request sees what the other writes afterwards: ``reserve`` copies a shared page before a
         request writes into it (copy-on-write)."""
-        if len(self.groups) != 1 or self.groups[0].need.window or self.state_layers:
+        if len(self.groups) != 1 or self.groups[0].need.window or self.groups[0].need.chunk or self.state_layers:
             raise RuntimeError("fork: only models with one full-attention group and no state can share pages")
         n = src.length if length is None else int(length)
         if src.closed or not (0 < n <= src.length):

@@ -1,9 +1,10 @@
 from .base import ConfigError, LayerSpec, ModelSpec, PartSpec, ScheduleEntry
 from .llama import LlamaConfig, RopeScaling, parse_rope_scaling
 from .nipadra import NipadraConfig
+from .gekupel import GekupelConfig
 from .registry import (Architecture, known_architectures, parse_config, register_architecture,
                        resolve_architecture)
 
-__all__ = ["ConfigError", "LayerSpec", "ModelSpec", "PartSpec", "ScheduleEntry", "LlamaConfig", "NipadraConfig",
+__all__ = ["ConfigError", "LayerSpec", "ModelSpec", "PartSpec", "ScheduleEntry", "LlamaConfig", "NipadraConfig", "GekupelConfig",
            "RopeScaling", "parse_rope_scaling", "Architecture", "known_architectures", "parse_config",
            "register_architecture", "resolve_architecture"]

@@ -71,11 +71,19 @@ class ModelSpec:
     # a design without a context length of its own: ``max_position`` is then only the engine's default, and the
     # caller's limit may exceed it
     open_ended: bool = False
+    # layer i -> layer j: layer i has no weights of its own and runs layer j's parts (its ``LayerSpec`` equals j's);
+    # its runs name ``layer`` j and ``cache_of`` i in the schedule, so that it keeps a cache or state of its own
+    shared_layers: Dict[int, int] = field(default_factory=dict)
 
     def validate(self) -> None:
         n = len(self.layers)
         if n == 0:
             raise ConfigError("a model needs at least one layer")
+        for i, j in self.shared_layers.items():
+            if not (0 <= i < n and 0 <= j < n) or j in self.shared_layers or i == j:
+                raise ConfigError(f"layer {i} cannot take the weights of layer {j}")
+            if self.layers[i] != self.layers[j]:
+                raise ConfigError(f"layer {i} takes the weights of layer {j} but is described differently")
         for e in self.schedule:
             if not (0 <= e.layer < n):
                 raise ConfigError(f"schedule names layer {e.layer}, the model has {n}")

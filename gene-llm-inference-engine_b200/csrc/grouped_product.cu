@@ -1,0 +1,339 @@
+// Matrix products whose weight matrix depends on the row: one matrix per head, or one per expert.
+//
+//   grouped_product   out[row, g-th slice] (=) W[g] a[row, g-th slice]  for tiles of 16 rows that share a group g
+//     heads    every row (token) runs through every group (head) h: a's columns a_off + h * a_gs .. + K,
+//              W[h] = w + h * w_gs [N, K], out's columns o_off + h * o_gs .. + N; optionally ``tail`` more
+//              columns behind a head's K inputs are rotated by the row's position and copied behind its N outputs
+//              (queries of an attention over a shared latent: the plain part goes through the head's key matrix,
+//              the rotated part stays)
+//     experts  rows are (token, choice) pairs sorted by expert: tile i belongs to expert tile_group[i], its rows are
+//              sorted_rows[16 i ..] (-1: none); the input row is pair / a_div, the output row the pair;
+//              gated: out = act(W_gate a) * (W_up a) with W[g] = [gate rows; up rows]
+//   route             per token: z = W_r x in 32-bit, s = sigmoid(z), the ``top`` experts by s + correction, weights s
+//   route_align       buckets the pairs by expert into tiles of 16 rows (padding with -1), one block
+//   route_combine     y[t] += sum_k weight[t, k] * part[t * top + k] in the order of k
+//
+// Products run on the CUDA cores with 32-bit fused multiply-adds in the order of k: the true 32-bit path, products of
+// few rows (decoding, where the expert weights stream once), and the bfloat16 path's fallback. An output element is
+// one chain of multiply-adds over its own row, whichever tile the row landed in.
+#include "common.cuh"
+
+namespace gi {
+
+constexpr int kGpTM = 16, kGpTN = 64, kGpTK = 32;
+
+struct GroupedArgs {
+    const void* a; long long lda; int a_off; int a_gs; int a_div;
+    const void* w; long long w_gs; int ldw; long long up_off;     // W[g] = w + g * w_gs, rows of ldw; the up rows start at up_off
+    void* out; int out_is_f32; long long ldo; int o_off; int o_gs;
+    int N, K, rows, groups;
+    const int* tile_group; const int* sorted_rows; const int* n_tiles;   // experts form (else null)
+    int act;                                                      // gated: 0 SiLU, 1 ReLU, 2 tanh-GELU
+    // rotated tail (heads form)
+    int tail; const float* freq; float amplitude; const int* positions;
+};
+
+__device__ __forceinline__ float gp_act(float g, int act) {
+    if (act == 1) return fmaxf(g, 0.f);
+    if (act == 2) return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+    return g * (1.0f / (1.0f + expf(-g)));
+}
+
+template <typename TA, typename TW, bool GATED>
+__global__ void __launch_bounds__(128)
+grouped_product_kernel(const GroupedArgs p) {
+    pdl_prologue();
+    constexpr int U = GATED ? 1 : 0;
+    __shared__ float s_a[kGpTK][kGpTM + 1];
+    __shared__ __align__(16) float s_w[U + 1][kGpTK][kGpTN + 4];
+    __shared__ int s_row[kGpTM];
+
+    const int tid = threadIdx.x;
+    int g, row0 = 0;
+    if (p.tile_group) {
+        if (static_cast<int>(blockIdx.x) >= *p.n_tiles) return;
+        g = p.tile_group[blockIdx.x];
+        if (tid < kGpTM) s_row[tid] = p.sorted_rows[blockIdx.x * kGpTM + tid];
+    } else {
+        g = blockIdx.x % p.groups;
+        row0 = (blockIdx.x / p.groups) * kGpTM;
+        if (tid < kGpTM) s_row[tid] = row0 + tid < p.rows ? row0 + tid : -1;
+    }
+    __syncthreads();
+    const int n0 = blockIdx.y * kGpTN;
+    const TA* A = static_cast<const TA*>(p.a);
+    const TW* W = static_cast<const TW*>(p.w) + static_cast<size_t>(g) * p.w_gs;
+
+    // rotated tail: only the blocks of the first tile of outputs do it
+    if (p.tail > 0 && blockIdx.y == 0) {
+        for (int i = tid; i < kGpTM * (p.tail / 2); i += 128) {
+            const int m = i / (p.tail / 2), pr = i % (p.tail / 2);
+            const int r = s_row[m];
+            if (r < 0) continue;
+            const TA* src = A + static_cast<size_t>(r) * p.lda + p.a_off + static_cast<size_t>(g) * p.a_gs + p.K + 2 * pr;
+            float sn, cs;
+            sincosf(static_cast<float>(p.positions[r]) * p.freq[pr], &sn, &cs);
+            sn *= p.amplitude; cs *= p.amplitude;
+            const float u = to_float(src[0]), v = to_float(src[1]);
+            const size_t o = static_cast<size_t>(r) * p.ldo + p.o_off + static_cast<size_t>(g) * p.o_gs + p.N + 2 * pr;
+            const float ru = u * cs - v * sn, rv = v * cs + u * sn;
+            if (p.out_is_f32) { static_cast<float*>(p.out)[o] = ru; static_cast<float*>(p.out)[o + 1] = rv; }
+            else { static_cast<__nv_bfloat16*>(p.out)[o] = __float2bfloat16_rn(ru); static_cast<__nv_bfloat16*>(p.out)[o + 1] = __float2bfloat16_rn(rv); }
+        }
+    }
+
+    const int tm = (tid >> 4) * 2, tn = (tid & 15) * 4;
+    float acc[2][4] = {}, acc_up[U + 1][4] = {};
+    for (int k0 = 0; k0 < p.K; k0 += kGpTK) {
+        // rows of a: 16 x 32 values
+        for (int i = tid; i < kGpTM * kGpTK; i += 128) {
+            const int m = i / kGpTK, k = i % kGpTK;
+            const int r = s_row[m];
+            float v = 0.f;
+            if (r >= 0 && k0 + k < p.K)
+                v = to_float(A[static_cast<size_t>(r / p.a_div) * p.lda + p.a_off + static_cast<size_t>(g) * p.a_gs + k0 + k]);
+            s_a[k][m] = v;
+        }
+        // rows of W: 64 x 32 values (and the up rows)
+        for (int i = tid; i < kGpTN * kGpTK; i += 128) {
+            const int n = i / kGpTK, k = i % kGpTK;
+            const bool in = n0 + n < p.N && k0 + k < p.K;
+            const size_t off = static_cast<size_t>(n0 + n) * p.ldw + k0 + k;
+            s_w[0][k][n] = in ? to_float(W[off]) : 0.f;
+            if (GATED) s_w[U][k][n] = in ? to_float(W[p.up_off + off]) : 0.f;
+        }
+        __syncthreads();
+#pragma unroll 8
+        for (int k = 0; k < kGpTK; ++k) {
+            const float a0 = s_a[k][tm], a1 = s_a[k][tm + 1];
+            const float4 w4 = *reinterpret_cast<const float4*>(&s_w[0][k][tn]);
+            acc[0][0] = fmaf(a0, w4.x, acc[0][0]); acc[0][1] = fmaf(a0, w4.y, acc[0][1]);
+            acc[0][2] = fmaf(a0, w4.z, acc[0][2]); acc[0][3] = fmaf(a0, w4.w, acc[0][3]);
+            acc[1][0] = fmaf(a1, w4.x, acc[1][0]); acc[1][1] = fmaf(a1, w4.y, acc[1][1]);
+            acc[1][2] = fmaf(a1, w4.z, acc[1][2]); acc[1][3] = fmaf(a1, w4.w, acc[1][3]);
+            if (GATED) {
+                const float4 u4 = *reinterpret_cast<const float4*>(&s_w[U][k][tn]);
+                acc_up[0][0] = fmaf(a0, u4.x, acc_up[0][0]); acc_up[0][1] = fmaf(a0, u4.y, acc_up[0][1]);
+                acc_up[0][2] = fmaf(a0, u4.z, acc_up[0][2]); acc_up[0][3] = fmaf(a0, u4.w, acc_up[0][3]);
+                acc_up[U][0] = fmaf(a1, u4.x, acc_up[U][0]); acc_up[U][1] = fmaf(a1, u4.y, acc_up[U][1]);
+                acc_up[U][2] = fmaf(a1, u4.z, acc_up[U][2]); acc_up[U][3] = fmaf(a1, u4.w, acc_up[U][3]);
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int r = s_row[tm + i];
+        if (r < 0) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int n = n0 + tn + j;
+            if (n >= p.N) continue;
+            float v = acc[i][j];
+            if (GATED) v = gp_act(v, p.act) * acc_up[U * i][j];
+            const size_t o = static_cast<size_t>(r) * p.ldo + p.o_off + static_cast<size_t>(g) * p.o_gs + n;
+            if (p.out_is_f32) static_cast<float*>(p.out)[o] = v;
+            else static_cast<__nv_bfloat16*>(p.out)[o] = __float2bfloat16_rn(v);
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ routing
+constexpr int kRouteMaxExperts = 1024;
+
+template <typename TX>
+__global__ void __launch_bounds__(128)
+route_kernel(const TX* __restrict__ x, int D, const float* __restrict__ w, const float* __restrict__ correction, int E, int top,
+             int* __restrict__ ids, float* __restrict__ weights) {
+    pdl_prologue();
+    extern __shared__ float s_x[];                 // [D]
+    __shared__ float s_score[kRouteMaxExperts], s_choice[kRouteMaxExperts];
+    const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (int d = threadIdx.x; d < D; d += 128) s_x[d] = to_float(x[static_cast<size_t>(t) * D + d]);
+    __syncthreads();
+    for (int e = warp; e < E; e += 4) {
+        const float* row = w + static_cast<size_t>(e) * D;
+        float z = 0.f;
+        for (int d = lane; d < D; d += 32) z = fmaf(row[d], s_x[d], z);
+        z = warp_sum(z);
+        if (lane == 0) {
+            const float s = 1.0f / (1.0f + expf(-z));
+            s_score[e] = s;
+            s_choice[e] = s + (correction ? correction[e] : 0.f);
+        }
+    }
+    __syncthreads();
+    if (warp != 0) return;
+    // the ``top`` largest choice scores, the lowest index among equals; a chosen expert leaves the contest
+    for (int k = 0; k < top; ++k) {
+        float best = -INFINITY;
+        int best_e = 0x7fffffff;
+        for (int e = lane; e < E; e += 32) {
+            const float c = s_choice[e];
+            if (c > best) { best = c; best_e = e; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+            if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; }
+        }
+        if (lane == 0) {
+            ids[static_cast<size_t>(t) * top + k] = best_e;
+            weights[static_cast<size_t>(t) * top + k] = s_score[best_e];
+            s_choice[best_e] = -INFINITY;
+        }
+        __syncwarp();
+    }
+}
+
+// One block: counts per expert, then tiles of 16 rows per expert in expert order.
+__global__ void __launch_bounds__(1024)
+route_align_kernel(const int* __restrict__ ids, int n_pairs, int E, int* __restrict__ sorted_rows, int* __restrict__ tile_group,
+                   int* __restrict__ n_tiles, int max_tiles) {
+    pdl_prologue();
+    __shared__ int s_count[kRouteMaxExperts], s_start[kRouteMaxExperts];
+    const int tid = threadIdx.x;
+    for (int e = tid; e < E; e += 1024) s_count[e] = 0;
+    for (int i = tid; i < max_tiles * kGpTM; i += 1024) sorted_rows[i] = -1;
+    __syncthreads();
+    for (int i = tid; i < n_pairs; i += 1024) atomicAdd(&s_count[ids[i]], 1);
+    __syncthreads();
+    if (tid == 0) {
+        int tiles = 0;
+        for (int e = 0; e < E; ++e) {
+            s_start[e] = tiles * kGpTM;
+            const int n = (s_count[e] + kGpTM - 1) / kGpTM;
+            for (int i = 0; i < n; ++i) tile_group[tiles + i] = e;
+            tiles += n;
+        }
+        *n_tiles = tiles;
+    }
+    __syncthreads();
+    // a pair takes the next free row of its expert (which row does not matter: an output element is computed from
+    // its own row alone, in the same order of operations in every row of a tile)
+    for (int i = tid; i < n_pairs; i += 1024) sorted_rows[atomicAdd(&s_start[ids[i]], 1)] = i;
+}
+
+__global__ void __launch_bounds__(256)
+route_combine_kernel(const float* __restrict__ part, const float* __restrict__ weights, float* __restrict__ y, int D, int top,
+                     size_t total) {
+    pdl_prologue();
+    const size_t i = static_cast<size_t>(blockIdx.x) * 256 + threadIdx.x;
+    if (i >= total) return;
+    const size_t t = i / D;
+    const int d = static_cast<int>(i % D);
+    float v = y[i];
+    for (int k = 0; k < top; ++k) v = fmaf(weights[t * top + k], part[(t * top + k) * D + d], v);
+    y[i] = v;
+}
+
+template <bool GATED>
+static int launch_grouped(const GroupedArgs& p, int a_dtype, int w_dtype, dim3 grid, cudaStream_t st) {
+    if (a_dtype == kF32 && w_dtype == kF32) launch_kernel((grouped_product_kernel<float, float, GATED>), grid, dim3(128), 0, st, p);
+    else if (a_dtype == kF32 && w_dtype == kBF16) launch_kernel((grouped_product_kernel<float, __nv_bfloat16, GATED>), grid, dim3(128), 0, st, p);
+    else if (a_dtype == kBF16 && w_dtype == kBF16) launch_kernel((grouped_product_kernel<__nv_bfloat16, __nv_bfloat16, GATED>), grid, dim3(128), 0, st, p);
+    else { set_error("grouped_product: inputs of dtype code %d with weights of %d are not built", a_dtype, w_dtype); return 2; }
+    return check_launch("grouped_product");
+}
+
+}  // namespace gi
+
+using namespace gi;
+
+extern "C" int gi_grouped_tile_rows() { return kGpTM; }
+
+static int gi_head_product_impl(const void* a, int a_dtype, long long lda, int a_off, int a_gs, const void* w, int w_dtype,
+                                long long w_gs, void* out, int out_dtype, long long ldo, int o_off, int o_gs, int rows, int heads,
+                                int N, int K, int tail, const float* freq, float amplitude, const int* positions, void* stream) {
+    if (rows == 0) return 0;
+    GI_REQUIRE(rows > 0 && heads > 0 && N > 0 && K > 0, "head_product: sizes must be positive");
+    GI_REQUIRE(tail >= 0 && tail % 2 == 0 && (tail == 0 || (freq && positions)), "head_product: a rotated tail needs an even size, frequencies and positions");
+    GI_REQUIRE(out_dtype == kF32 || out_dtype == kBF16, "head_product: unsupported output dtype");
+    GroupedArgs p = {};
+    p.a = a; p.lda = lda; p.a_off = a_off; p.a_gs = a_gs; p.a_div = 1;
+    p.w = w; p.w_gs = w_gs; p.ldw = K; p.up_off = 0;
+    p.out = out; p.out_is_f32 = out_dtype == kF32; p.ldo = ldo; p.o_off = o_off; p.o_gs = o_gs;
+    p.N = N; p.K = K; p.rows = rows; p.groups = heads;
+    p.tail = tail; p.freq = freq; p.amplitude = amplitude; p.positions = positions;
+    const long long tiles = static_cast<long long>((rows + kGpTM - 1) / kGpTM) * heads;
+    GI_REQUIRE(tiles <= 2147483647LL, "head_product: too many tiles");
+    dim3 grid(static_cast<unsigned>(tiles), (N + kGpTN - 1) / kGpTN);
+    return launch_grouped<false>(p, a_dtype, w_dtype, grid, static_cast<cudaStream_t>(stream));
+}
+
+static int gi_expert_product_impl(const void* a, int a_dtype, long long lda, int a_div, const void* w, int w_dtype, long long w_gs,
+                                  int ldw, long long up_off, int gated, int act, void* out, int out_dtype, long long ldo,
+                                  int N, int K, const int* tile_group, const int* sorted_rows, const int* n_tiles, int max_tiles,
+                                  void* stream) {
+    if (max_tiles == 0) return 0;
+    GI_REQUIRE(max_tiles > 0 && N > 0 && K > 0 && a_div > 0, "expert_product: sizes must be positive");
+    GI_REQUIRE(tile_group && sorted_rows && n_tiles, "expert_product: the sorted rows are missing");
+    GI_REQUIRE(act >= 0 && act <= 2, "expert_product: unknown activation code %d", act);
+    GroupedArgs p = {};
+    p.a = a; p.lda = lda; p.a_div = a_div;
+    p.w = w; p.w_gs = w_gs; p.ldw = ldw; p.up_off = up_off;
+    p.out = out; p.out_is_f32 = out_dtype == kF32; p.ldo = ldo;
+    p.N = N; p.K = K; p.groups = 1;
+    p.tile_group = tile_group; p.sorted_rows = sorted_rows; p.n_tiles = n_tiles; p.act = act;
+    dim3 grid(max_tiles, (N + kGpTN - 1) / kGpTN);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    return gated ? launch_grouped<true>(p, a_dtype, w_dtype, grid, st) : launch_grouped<false>(p, a_dtype, w_dtype, grid, st);
+}
+
+static int gi_route_impl(const void* x, int x_dtype, int T, int D, const float* w, const float* correction, int E, int top,
+                         int* ids, float* weights, int* sorted_rows, int* tile_group, int* n_tiles, int max_tiles, void* stream) {
+    if (T == 0) return 0;
+    GI_REQUIRE(T > 0 && D > 0 && E > 0 && top > 0 && top <= E, "route: sizes must be positive and top at most the experts");
+    GI_REQUIRE(E <= kRouteMaxExperts, "route: %d experts exceed %d", E, kRouteMaxExperts);
+    GI_REQUIRE(static_cast<size_t>(D) * 4 <= 160 * 1024, "route: a row of %d values does not fit shared memory", D);
+    const long long pairs = static_cast<long long>(T) * top;
+    GI_REQUIRE(max_tiles >= (pairs + kGpTM - 1) / kGpTM + std::min<long long>(E, pairs) - 1, "route: room for %d tiles is too little", max_tiles);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const size_t smem = static_cast<size_t>(D) * 4;
+    if (x_dtype == kF32) {
+        if (smem > 40 * 1024) cudaFuncSetAttribute(route_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+        launch_kernel((route_kernel<float>), dim3(T), dim3(128), smem, st, static_cast<const float*>(x), D, w, correction, E, top, ids, weights);
+    } else if (x_dtype == kBF16) {
+        if (smem > 40 * 1024) cudaFuncSetAttribute(route_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+        launch_kernel((route_kernel<__nv_bfloat16>), dim3(T), dim3(128), smem, st, static_cast<const __nv_bfloat16*>(x), D, w, correction, E, top, ids, weights);
+    } else {
+        GI_REQUIRE(false, "route: unsupported dtype code %d", x_dtype);
+    }
+    if (check_launch("route")) return 1;
+    launch_kernel(route_align_kernel, dim3(1), dim3(1024), 0, st, static_cast<const int*>(ids), static_cast<int>(pairs), E, sorted_rows, tile_group, n_tiles, max_tiles);
+    return check_launch("route_align");
+}
+
+static int gi_route_combine_impl(const float* part, const float* weights, float* y, int T, int D, int top, void* stream) {
+    if (T == 0) return 0;
+    GI_REQUIRE(T > 0 && D > 0 && top > 0, "route_combine: sizes must be positive");
+    const size_t total = static_cast<size_t>(T) * D;
+    launch_kernel(route_combine_kernel, dim3(static_cast<unsigned>((total + 255) / 256)), dim3(256), 0, static_cast<cudaStream_t>(stream),
+                  part, weights, y, D, top, total);
+    return check_launch("route_combine");
+}
+
+extern "C" int gi_head_product(const void* a, int a_dtype, long long lda, int a_off, int a_gs, const void* w, int w_dtype,
+                               long long w_gs, void* out, int out_dtype, long long ldo, int o_off, int o_gs, int rows, int heads,
+                               int N, int K, int tail, const float* freq, float amplitude, const int* positions, void* stream) {
+    return gi::dispatch(gi_head_product_impl, a, a_dtype, lda, a_off, a_gs, w, w_dtype, w_gs, out, out_dtype, ldo, o_off, o_gs, rows,
+                        heads, N, K, tail, freq, amplitude, positions, stream);
+}
+
+extern "C" int gi_expert_product(const void* a, int a_dtype, long long lda, int a_div, const void* w, int w_dtype, long long w_gs,
+                                 int ldw, long long up_off, int gated, int act, void* out, int out_dtype, long long ldo, int N, int K,
+                                 const int* tile_group, const int* sorted_rows, const int* n_tiles, int max_tiles, void* stream) {
+    return gi::dispatch(gi_expert_product_impl, a, a_dtype, lda, a_div, w, w_dtype, w_gs, ldw, up_off, gated, act, out, out_dtype, ldo,
+                        N, K, tile_group, sorted_rows, n_tiles, max_tiles, stream);
+}
+
+extern "C" int gi_route(const void* x, int x_dtype, int T, int D, const float* w, const float* correction, int E, int top, int* ids,
+                        float* weights, int* sorted_rows, int* tile_group, int* n_tiles, int max_tiles, void* stream) {
+    return gi::dispatch(gi_route_impl, x, x_dtype, T, D, w, correction, E, top, ids, weights, sorted_rows, tile_group, n_tiles,
+                        max_tiles, stream);
+}
+
+extern "C" int gi_route_combine(const float* part, const float* weights, float* y, int T, int D, int top, void* stream) {
+    return gi::dispatch(gi_route_combine_impl, part, weights, y, T, D, top, stream);
+}

@@ -12,6 +12,13 @@
 //                   them come from any column of the same input row (the keys as projected, for a design whose
 //                   values are its keys).
 //
+//   add_normed      x += w * (y / sqrt(mean(y^2) + eps)): a layer whose norm stands on the sublayer's output. The same
+//                   pass leaves xn = x in the compute dtype (what the next sublayer reads) and clears y (what it
+//                   adds its output to)
+//   latent_store    per token, from one row of 32-bit projections: a query latent brought to unit RMS and weighted,
+//                   to q_latent; a key/value latent likewise, into the first columns of the token's page row; a
+//                   rotated part shared by all heads (angles position * freq[i], cos and sin times a constant) behind it
+//
 // All arithmetic is 32-bit; only stores round. A row's result depends on that row only.
 #include "common.cuh"
 
@@ -119,7 +126,7 @@ norm_rope_store_kernel(const float* __restrict__ in, int ld, int q_off, int k_of
                        const int* __restrict__ positions, const int* __restrict__ row_req,
                        const int* __restrict__ block_tables, int table_stride,
                        T* __restrict__ q_out, T* __restrict__ k_cache, T* __restrict__ v_cache,
-                       int H, int Hkv, int hd, int page_size, int write_kv) {
+                       int H, int Hkv, int hd, int vd, int page_size, int write_kv) {
     pdl_prologue();
     __shared__ float s_cos[kNrsMaxHead / 2], s_sin[kNrsMaxHead / 2];
     const int t = blockIdx.x;
@@ -129,10 +136,11 @@ norm_rope_store_kernel(const float* __restrict__ in, int ld, int q_off, int k_of
     for (int i = threadIdx.x; i < half; i += kNrsWarps * 32) sincosf(static_cast<float>(pos) * freq[i], &s_sin[i], &s_cos[i]);
     __syncthreads();
     const float* row = in + static_cast<size_t>(t) * ld;
-    size_t kv_base = 0;
+    size_t kv_base = 0, v_base = 0;       // in rows: a value row has vd values, a key row hd
     if (write_kv) {
         const int page = block_tables[static_cast<size_t>(row_req[t]) * table_stride + pos / page_size];
         kv_base = (static_cast<size_t>(page) * Hkv * page_size + (pos % page_size)) * hd;
+        v_base = (static_cast<size_t>(page) * Hkv * page_size + (pos % page_size)) * vd;
     }
     const int n_heads = H + (write_kv ? Hkv : 0);
     const int n_pairs = hd / 2;
@@ -163,9 +171,9 @@ norm_rope_store_kernel(const float* __restrict__ in, int ld, int q_off, int k_of
                       : k_cache + kv_base + static_cast<size_t>(head - H) * page_size * hd;
         if (!is_q) {
             // the values: copied from their columns as they are (the keys themselves where the design says so)
-            const float* vsrc = row + v_off + (head - H) * hd;
-            T* vdst = v_cache + kv_base + static_cast<size_t>(head - H) * page_size * hd;
-            for (int d = lane; d < hd; d += 32) vdst[d] = from_float<T>(vsrc[d]);
+            const float* vsrc = row + v_off + (head - H) * vd;
+            T* vdst = v_cache + v_base + static_cast<size_t>(head - H) * page_size * vd;
+            for (int d = lane; d < vd; d += 32) vdst[d] = from_float<T>(vsrc[d]);
         }
         if (nw) {
             ss = warp_sum(ss);
@@ -191,6 +199,63 @@ norm_rope_store_kernel(const float* __restrict__ in, int ld, int q_off, int k_of
             dst[ia[u]] = from_float<T>(a);
             dst[ib[u]] = from_float<T>(b);
         }
+    }
+}
+
+template <typename TOut>
+__global__ void __launch_bounds__(256)
+add_normed_kernel(float* __restrict__ y, const float* __restrict__ weight, float* __restrict__ x, TOut* __restrict__ xn_out,
+                  int D, float eps, int clear_y) {
+    pdl_prologue();
+    __shared__ float warp_part[8];
+    const size_t row = static_cast<size_t>(blockIdx.x) * D;
+    float ss = 0.f;
+    for (int d = threadIdx.x; d < D; d += 256) ss = fmaf(y[row + d], y[row + d], ss);
+    const float total = block_sum_256(ss, warp_part);
+    const float scale = 1.0f / sqrtf(total / static_cast<float>(D) + eps);
+    for (int d = threadIdx.x; d < D; d += 256) {
+        const float v = x[row + d] + weight[d] * (scale * y[row + d]);
+        x[row + d] = v;
+        if (xn_out) xn_out[row + d] = from_float<TOut>(v);
+        if (clear_y) y[row + d] = 0.f;
+    }
+}
+
+// One block per token. The two latents are normed by the block (sums in the order of block_sum_256); the rotated part
+// is a pair per thread.
+template <typename T>
+__global__ void __launch_bounds__(256)
+latent_store_kernel(const float* __restrict__ in, int ld, int q_off, int q_rank, const float* __restrict__ q_weight,
+                    T* __restrict__ q_latent, int c_off, int rank, const float* __restrict__ c_weight, int r_off, int rot,
+                    const float* __restrict__ freq, float amplitude, float eps, const int* __restrict__ positions,
+                    const int* __restrict__ row_req, const int* __restrict__ block_tables, int table_stride,
+                    T* __restrict__ cache, int page_size, int write_cache) {
+    pdl_prologue();
+    __shared__ float warp_part[8];
+    const int t = blockIdx.x;
+    const float* row = in + static_cast<size_t>(t) * ld;
+    if (q_latent) {
+        float ss = 0.f;
+        for (int d = threadIdx.x; d < q_rank; d += 256) ss = fmaf(row[q_off + d], row[q_off + d], ss);
+        const float scale = 1.0f / sqrtf(block_sum_256(ss, warp_part) / static_cast<float>(q_rank) + eps);
+        for (int d = threadIdx.x; d < q_rank; d += 256)
+            q_latent[static_cast<size_t>(t) * q_rank + d] = from_float<T>(q_weight[d] * (scale * row[q_off + d]));
+    }
+    if (!write_cache) return;
+    const int pos = positions[t];
+    const int page = block_tables[static_cast<size_t>(row_req[t]) * table_stride + pos / page_size];
+    T* dst = cache + (static_cast<size_t>(page) * page_size + (pos % page_size)) * (rank + rot);
+    float ss = 0.f;
+    for (int d = threadIdx.x; d < rank; d += 256) ss = fmaf(row[c_off + d], row[c_off + d], ss);
+    const float scale = 1.0f / sqrtf(block_sum_256(ss, warp_part) / static_cast<float>(rank) + eps);
+    for (int d = threadIdx.x; d < rank; d += 256) dst[d] = from_float<T>(c_weight[d] * (scale * row[c_off + d]));
+    for (int pr = threadIdx.x; pr < rot / 2; pr += 256) {
+        float sn, cs;
+        sincosf(static_cast<float>(pos) * freq[pr], &sn, &cs);
+        sn *= amplitude; cs *= amplitude;
+        const float u = row[r_off + 2 * pr], v = row[r_off + 2 * pr + 1];
+        dst[rank + 2 * pr] = from_float<T>(u * cs - v * sn);
+        dst[rank + 2 * pr + 1] = from_float<T>(v * cs + u * sn);
     }
 }
 
@@ -253,12 +318,13 @@ static int gi_norm_rope_store_impl(const float* in, int ld, int q_off, int k_off
                                    const float* k_norm, float eps, const float* freq, int rot_half, int interleaved,
                                    const int* positions, const int* row_req, const int* block_tables, int table_stride,
                                    void* q_out, void* k_cache, void* v_cache, int dtype, int T, int H, int Hkv, int hd,
-                                   int page_size, int write_kv, void* stream) {
+                                   int vd, int page_size, int write_kv, void* stream) {
     if (T == 0) return 0;
     GI_REQUIRE(T > 0 && H > 0 && Hkv > 0 && hd > 0 && page_size > 0, "norm_rope_store: sizes must be positive");
     GI_REQUIRE(hd <= kNrsMaxHead && hd % 2 == 0, "norm_rope_store: head size %d is odd or exceeds %d", hd, kNrsMaxHead);
     GI_REQUIRE(2 * rot_half <= hd, "norm_rope_store: rotary size %d exceeds the head size %d", 2 * rot_half, hd);
-    GI_REQUIRE(q_off >= 0 && k_off >= 0 && v_off >= 0 && q_off + H * hd <= ld && k_off + Hkv * hd <= ld && v_off + Hkv * hd <= ld,
+    GI_REQUIRE(vd > 0, "norm_rope_store: the value size must be positive");
+    GI_REQUIRE(q_off >= 0 && k_off >= 0 && v_off >= 0 && q_off + H * hd <= ld && k_off + Hkv * hd <= ld && v_off + Hkv * vd <= ld,
                "norm_rope_store: the columns of queries, keys or values lie outside the input row of %d", ld);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     GI_REQUIRE(T <= 2147483647, "norm_rope_store: too many rows");
@@ -268,12 +334,12 @@ static int gi_norm_rope_store_impl(const float* in, int ld, int q_off, int k_off
         launch_kernel((norm_rope_store_kernel<float>), dim3(T, head_blocks), dim3(kNrsWarps * 32), 0, st, in, ld, q_off, k_off, v_off, q_norm,
                       k_norm, eps, freq, rot_half, interleaved, positions, row_req, block_tables, table_stride,
                       static_cast<float*>(q_out), static_cast<float*>(k_cache), static_cast<float*>(v_cache), H, Hkv, hd,
-                      page_size, write_kv);
+                      vd, page_size, write_kv);
     else if (dtype == kBF16)
         launch_kernel((norm_rope_store_kernel<__nv_bfloat16>), dim3(T, head_blocks), dim3(kNrsWarps * 32), 0, st, in, ld, q_off, k_off, v_off,
                       q_norm, k_norm, eps, freq, rot_half, interleaved, positions, row_req, block_tables, table_stride,
                       static_cast<__nv_bfloat16*>(q_out), static_cast<__nv_bfloat16*>(k_cache),
-                      static_cast<__nv_bfloat16*>(v_cache), H, Hkv, hd, page_size, write_kv);
+                      static_cast<__nv_bfloat16*>(v_cache), H, Hkv, hd, vd, page_size, write_kv);
     else
         GI_REQUIRE(false, "norm_rope_store: unsupported dtype code %d", dtype);
     return check_launch("norm_rope_store");
@@ -291,6 +357,49 @@ extern "C" int gi_gated_act(const float* gate_up, void* out, int out_dtype, int 
     return gi::dispatch(gi_gated_act_impl, gate_up, out, out_dtype, T, I, act, stream);
 }
 
-extern "C" int gi_norm_rope_store(const float* in, int ld, int q_off, int k_off, int v_off, const float* q_norm, const float* k_norm, float eps, const float* freq, int rot_half, int interleaved, const int* positions, const int* row_req, const int* block_tables, int table_stride, void* q_out, void* k_cache, void* v_cache, int dtype, int T, int H, int Hkv, int hd, int page_size, int write_kv, void* stream) {
-    return gi::dispatch(gi_norm_rope_store_impl, in, ld, q_off, k_off, v_off, q_norm, k_norm, eps, freq, rot_half, interleaved, positions, row_req, block_tables, table_stride, q_out, k_cache, v_cache, dtype, T, H, Hkv, hd, page_size, write_kv, stream);
+extern "C" int gi_norm_rope_store(const float* in, int ld, int q_off, int k_off, int v_off, const float* q_norm, const float* k_norm, float eps, const float* freq, int rot_half, int interleaved, const int* positions, const int* row_req, const int* block_tables, int table_stride, void* q_out, void* k_cache, void* v_cache, int dtype, int T, int H, int Hkv, int hd, int vd, int page_size, int write_kv, void* stream) {
+    return gi::dispatch(gi_norm_rope_store_impl, in, ld, q_off, k_off, v_off, q_norm, k_norm, eps, freq, rot_half, interleaved, positions, row_req, block_tables, table_stride, q_out, k_cache, v_cache, dtype, T, H, Hkv, hd, vd, page_size, write_kv, stream);
+}
+
+static int gi_add_normed_impl(float* y, const float* weight, float* x, void* xn_out, int xn_dtype, int rows, int D, float eps,
+                              int clear_y, void* stream) {
+    if (rows == 0) return 0;
+    GI_REQUIRE(rows > 0 && D > 0, "add_normed: sizes must be positive (rows=%d, D=%d)", rows, D);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (xn_dtype == kBF16)
+        launch_kernel((add_normed_kernel<__nv_bfloat16>), dim3(rows), dim3(256), 0, st, y, weight, x, static_cast<__nv_bfloat16*>(xn_out), D, eps, clear_y);
+    else
+        launch_kernel((add_normed_kernel<float>), dim3(rows), dim3(256), 0, st, y, weight, x, static_cast<float*>(xn_out), D, eps, clear_y);
+    return check_launch("add_normed");
+}
+
+static int gi_latent_store_impl(const float* in, int ld, int q_off, int q_rank, const float* q_weight, void* q_latent, int c_off,
+                                int rank, const float* c_weight, int r_off, int rot, const float* freq, float amplitude, float eps,
+                                const int* positions, const int* row_req, const int* block_tables, int table_stride, void* cache,
+                                int dtype, int T, int page_size, int write_cache, void* stream) {
+    if (T == 0) return 0;
+    GI_REQUIRE(T > 0 && rank > 0 && rot >= 0 && rot % 2 == 0 && page_size > 0, "latent_store: sizes must be positive and the rotated part even");
+    GI_REQUIRE(q_latent == nullptr || (q_rank > 0 && q_weight && q_off >= 0 && q_off + q_rank <= ld), "latent_store: the query latent lies outside the row");
+    GI_REQUIRE(c_off >= 0 && c_off + rank <= ld && r_off >= 0 && r_off + rot <= ld, "latent_store: the key/value latent lies outside the row of %d", ld);
+    GI_REQUIRE(rot == 0 || freq, "latent_store: the rotated part needs frequencies");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (dtype == kF32)
+        launch_kernel((latent_store_kernel<float>), dim3(T), dim3(256), 0, st, in, ld, q_off, q_rank, q_weight, static_cast<float*>(q_latent),
+                      c_off, rank, c_weight, r_off, rot, freq, amplitude, eps, positions, row_req, block_tables, table_stride,
+                      static_cast<float*>(cache), page_size, write_cache);
+    else if (dtype == kBF16)
+        launch_kernel((latent_store_kernel<__nv_bfloat16>), dim3(T), dim3(256), 0, st, in, ld, q_off, q_rank, q_weight,
+                      static_cast<__nv_bfloat16*>(q_latent), c_off, rank, c_weight, r_off, rot, freq, amplitude, eps, positions, row_req,
+                      block_tables, table_stride, static_cast<__nv_bfloat16*>(cache), page_size, write_cache);
+    else
+        GI_REQUIRE(false, "latent_store: unsupported dtype code %d", dtype);
+    return check_launch("latent_store");
+}
+
+extern "C" int gi_add_normed(float* y, const float* weight, float* x, void* xn_out, int xn_dtype, int rows, int D, float eps, int clear_y, void* stream) {
+    return gi::dispatch(gi_add_normed_impl, y, weight, x, xn_out, xn_dtype, rows, D, eps, clear_y, stream);
+}
+
+extern "C" int gi_latent_store(const float* in, int ld, int q_off, int q_rank, const float* q_weight, void* q_latent, int c_off, int rank, const float* c_weight, int r_off, int rot, const float* freq, float amplitude, float eps, const int* positions, const int* row_req, const int* block_tables, int table_stride, void* cache, int dtype, int T, int page_size, int write_cache, void* stream) {
+    return gi::dispatch(gi_latent_store_impl, in, ld, q_off, q_rank, q_weight, q_latent, c_off, rank, c_weight, r_off, rot, freq, amplitude, eps, positions, row_req, block_tables, table_stride, cache, dtype, T, page_size, write_cache, stream);
 }

@@ -81,7 +81,8 @@ class StepContext:
         self.longest_single = min(engine.model.max_position, rounded)
 
     def pages(self, layer: int) -> Tuple[torch.Tensor, torch.Tensor]:
-        """(keys, values) of a layer, each [pages, Hkv, page_size, head_dim]."""
+        """(keys, values) of a layer: [pages, Hkv, page_size, head_dim] and [pages, Hkv, page_size, value width]
+        (values None for a layer whose values are read out of its key rows)."""
         return self._engine.layer_pages[layer]
 
     def block_tables(self, layer: int) -> torch.Tensor:
@@ -206,16 +207,26 @@ class StepEngine:
         self.cache = CacheManager(needs, page_size, n_pages, model.max_position, max_requests,
                                   state_layers=sorted(state_needs))
         # device memory of the pages: per group [layers of the group, 2 (keys, values), pages, Hkv, page, hd]
+        # (a group whose values have a width of their own keeps them in a second tensor [layers, 1, pages, Hkv, page, vd],
+        # one whose values lie in the key rows has none)
         self.group_pages: List[torch.Tensor] = []
-        self.layer_pages: Dict[int, Tuple[torch.Tensor, torch.Tensor]] = {}
+        self.group_value_pages: List[Optional[torch.Tensor]] = []
+        self.layer_pages: Dict[int, Tuple[torch.Tensor, Optional[torch.Tensor]]] = {}
         for group in self.cache.groups:
             need = group.need
-            t = torch.empty((len(group.layers), 2, n_pages, need.num_kv_heads, page_size, need.head_dim),
+            same = need.value_width == need.head_dim
+            t = torch.empty((len(group.layers), 2 if same else 1, n_pages, need.num_kv_heads, page_size, need.head_dim),
                             dtype=model.dtype, device=self.device)
             t.fill_(float("nan"))       # never read before written; NaN makes a stale read visible
             self.group_pages.append(t)
+            v = None
+            if not same and need.value_width > 0:
+                v = torch.empty((len(group.layers), 1, n_pages, need.num_kv_heads, page_size, need.value_width),
+                                dtype=model.dtype, device=self.device)
+                v.fill_(float("nan"))
+            self.group_value_pages.append(v)
             for i, layer in enumerate(group.layers):
-                self.layer_pages[layer] = (t[i, 0], t[i, 1])
+                self.layer_pages[layer] = (t[i, 0], t[i, 1] if same else (v[i, 0] if v is not None else None))
         self.layer_state: Dict[int, torch.Tensor] = {}
         for layer, need in state_needs.items():
             self.layer_state[layer] = torch.zeros((max_requests, *need.shape), dtype=_STATE_DTYPES[need.dtype],
@@ -520,7 +531,7 @@ class StepEngine:
             rc = self.cache.requests[seg.key]
             for g, group in enumerate(self.cache.groups):
                 table = host[self._table_off[g] + r * self._table_stride:self._table_off[g] + (r + 1) * self._table_stride]
-                first = rc.first_live[g] if group.need.window else 0
+                first = rc.first_live[g] if (group.need.window or group.need.chunk) else 0
                 used = table[first:(seg.first_position + seg.length + ps - 1) // ps]
                 if ((used < 0) | (used >= self.n_pages)).any():
                     raise AssertionError(f"step descriptor: request {seg.key!r} names a page outside the pool of {self.n_pages}")
@@ -577,5 +588,6 @@ class StepEngine:
                 continue
             src = torch.tensor([c.src for c in mine], dtype=torch.int32, device=self.device)
             dst = torch.tensor([c.dst for c in mine], dtype=torch.int32, device=self.device)
-            flat = pages.view(pages.shape[0] * 2, *pages.shape[2:])
-            kernels.copy_pages(flat, src, dst)
+            for t in (pages, self.group_value_pages[g]):
+                if t is not None:
+                    kernels.copy_pages(t.view(t.shape[0] * t.shape[1], *t.shape[2:]), src, dst)

@@ -232,19 +232,20 @@ def norm_rope_store(proj: torch.Tensor, q_offset: int, k_offset: int, v_offset: 
                     k_norm: Optional[torch.Tensor], eps: float, freq: Optional[torch.Tensor], interleaved: bool,
                     positions: torch.Tensor, row_req: torch.Tensor, block_tables: torch.Tensor, q_out: torch.Tensor,
                     k_cache: torch.Tensor, v_cache: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int,
-                    page_size: int, write_kv: bool = True) -> None:
+                    page_size: int, write_kv: bool = True, value_dim: Optional[int] = None) -> None:
     """From the 32-bit projections ``proj`` [T, ld] (query heads from column q_offset, key heads from k_offset,
     value heads from v_offset, which may be the keys' columns): per head an optional unit-RMS norm with the
     shared weight ``q_norm`` / ``k_norm`` [hd], then the rotation of the first 2 * len(freq) dimensions by
     position * freq[i] (angles computed on the device in 32-bit), queries to ``q_out`` [T, H*hd], keys and
-    values into the token's page row."""
+    values into the token's page row. ``value_dim``: the width of a value head when it is not the head size."""
     T, ld = proj.shape
+    vd = head_dim if value_dim is None else int(value_dim)
     if q_out.shape != (T, num_heads * head_dim):
         raise KernelError("norm_rope_store: q_out must be [T, H*hd]")
     if k_cache.dtype != q_out.dtype or v_cache.dtype != q_out.dtype:
         raise KernelError("norm_rope_store: q_out and the cache must have one dtype")
-    if k_cache.shape[1:] != (num_kv_heads, page_size, head_dim) or v_cache.shape != k_cache.shape:
-        raise KernelError("norm_rope_store: the cache must be [pages, Hkv, page_size, hd]")
+    if k_cache.shape[1:] != (num_kv_heads, page_size, head_dim) or v_cache.shape != (k_cache.shape[0], num_kv_heads, page_size, vd):
+        raise KernelError("norm_rope_store: the cache must be [pages, Hkv, page_size, hd] (values: their own width)")
     for w, name in ((q_norm, "q_norm"), (k_norm, "k_norm")):
         if w is not None and w.numel() != head_dim:
             raise KernelError(f"norm_rope_store: {name} must have head_dim values")
@@ -255,7 +256,158 @@ def norm_rope_store(proj: torch.Tensor, q_offset: int, k_offset: int, v_offset: 
         _dev(positions, "positions", torch.int32), _dev(row_req, "row_req", torch.int32),
         _dev(block_tables, "block_tables", torch.int32), block_tables.shape[1], _dev(q_out, "q_out"),
         _dev(k_cache, "k_cache"), _dev(v_cache, "v_cache"), dtype_code(q_out.dtype), T, num_heads, num_kv_heads,
-        head_dim, page_size, int(write_kv), _stream()), "norm_rope_store")
+        head_dim, vd, page_size, int(write_kv), _stream()), "norm_rope_store")
+
+
+def add_normed(y: torch.Tensor, weight: torch.Tensor, x: torch.Tensor, eps: float, xn_out: Optional[torch.Tensor] = None,
+               clear_y: bool = False) -> None:
+    """x += weight * (y / sqrt(mean(y^2) + eps)) per row, in 32-bit; optionally also xn_out = x in xn_out's dtype and
+    y = 0: what the next sublayer of a layer whose norms stand on the sublayers' outputs reads and adds to."""
+    n, D = y.shape
+    if x.shape != y.shape or weight.numel() != D or (xn_out is not None and xn_out.shape != y.shape):
+        raise KernelError("add_normed: shapes of y, weight, x and xn_out do not agree")
+    check(lib().gi_add_normed(_dev(y, "y", torch.float32), _dev(weight, "weight", torch.float32), _dev(x, "x", torch.float32),
+                              0 if xn_out is None else _dev(xn_out, "xn_out"), F32 if xn_out is None else dtype_code(xn_out.dtype),
+                              n, D, float(eps), int(bool(clear_y)), _stream()), "add_normed")
+
+
+def latent_store(proj: torch.Tensor, q_offset: int, q_weight: Optional[torch.Tensor], q_latent: Optional[torch.Tensor],
+                 c_offset: int, c_weight: torch.Tensor, rot_offset: int, freq: Optional[torch.Tensor], amplitude: float,
+                 eps: float, positions: torch.Tensor, row_req: torch.Tensor, block_tables: torch.Tensor, cache: torch.Tensor,
+                 page_size: int, write_cache: bool = True) -> None:
+    """From the 32-bit projections ``proj`` [T, ld]: the query latent (columns from q_offset, len(q_weight) wide) is
+    brought to unit RMS, weighted and written to ``q_latent`` [T, q_rank]; the key/value latent (from c_offset,
+    len(c_weight) wide) likewise into the first columns of the token's page row of ``cache`` [pages, 1, page_size,
+    rank + rot]; the 2 * len(freq) columns from rot_offset are rotated pair by pair (2i, 2i+1) by position * freq[i],
+    cos and sin times ``amplitude``, and written behind it."""
+    T, ld = proj.shape
+    rank = c_weight.numel()
+    rot = 0 if freq is None else 2 * freq.numel()
+    if cache.dim() != 4 or cache.shape[1:] != (1, page_size, rank + rot):
+        raise KernelError("latent_store: the cache must be [pages, 1, page_size, rank + rot]")
+    if q_latent is not None and (q_weight is None or q_latent.shape != (T, q_weight.numel()) or q_latent.dtype != cache.dtype):
+        raise KernelError("latent_store: q_latent must be [T, q_rank] of the cache's dtype")
+    check(lib().gi_latent_store(
+        _dev(proj, "proj", torch.float32), ld, int(q_offset), 0 if q_weight is None else q_weight.numel(),
+        _opt(q_weight, "q_weight", torch.float32), 0 if q_latent is None else _dev(q_latent, "q_latent"), int(c_offset), rank,
+        _dev(c_weight, "c_weight", torch.float32), int(rot_offset), rot, _opt(freq, "freq", torch.float32), float(amplitude),
+        float(eps), _dev(positions, "positions", torch.int32), _dev(row_req, "row_req", torch.int32),
+        _dev(block_tables, "block_tables", torch.int32), block_tables.shape[1], _dev(cache, "cache"), dtype_code(cache.dtype), T,
+        page_size, int(write_cache), _stream()), "latent_store")
+
+
+def attention_rows_supported(head_dim: int, value_dim: int) -> bool:
+    """Whether the row-form attention kernel serves these sizes."""
+    return bool(lib().gi_attention_rows_supported(int(head_dim), int(value_dim)))
+
+
+def attention_rows(q: torch.Tensor, k_cache: torch.Tensor, v_cache: Optional[torch.Tensor], out: torch.Tensor,
+                   row_req: torch.Tensor, positions: torch.Tensor, block_tables: torch.Tensor, num_heads: int,
+                   num_kv_heads: int, head_dim: int, value_dim: int, page_size: int, scale: float,
+                   window: Optional[int] = None, chunk: Optional[int] = None, slopes: Optional[torch.Tensor] = None,
+                   sinks: Optional[torch.Tensor] = None) -> None:
+    """Attention of every row of ``q`` [T, H*hd] (32-bit or bfloat16) over its request's pages, 32-bit arithmetic.
+    ``v_cache`` None: the values are the first ``value_dim`` columns of the key rows. ``window``: the last w positions;
+    ``chunk``: only keys of the query's own block of c positions; ``slopes`` [H]: slope_h * distance is taken off a
+    score; ``sinks`` [H]: exp(sinks_h) more in the softmax's denominator. ``out`` [T, H*vd], 32-bit or bfloat16."""
+    T = q.shape[0]
+    if q.dim() != 2 or q.shape[1] != num_heads * head_dim or out.shape != (T, num_heads * value_dim):
+        raise KernelError("attention_rows: q must be [T, H*hd] and out [T, H*vd]")
+    if k_cache.dim() != 4 or k_cache.shape[1:] != (num_kv_heads, page_size, head_dim):
+        raise KernelError("attention_rows: the keys must be [pages, Hkv, page_size, hd]")
+    if v_cache is not None and (v_cache.shape != (k_cache.shape[0], num_kv_heads, page_size, value_dim) or v_cache.dtype != k_cache.dtype):
+        raise KernelError("attention_rows: the values must be [pages, Hkv, page_size, vd] of the keys' dtype")
+    for t, name in ((slopes, "slopes"), (sinks, "sinks")):
+        if t is not None and t.numel() != num_heads:
+            raise KernelError(f"attention_rows: {name} must have one value per head")
+    check(lib().gi_attention_rows(
+        _dev(q, "q"), dtype_code(q.dtype), q.shape[1], _dev(k_cache, "k_cache"), 0 if v_cache is None else _dev(v_cache, "v_cache"),
+        dtype_code(k_cache.dtype), _dev(out, "out"), dtype_code(out.dtype), out.shape[1], _dev(row_req, "row_req", torch.int32),
+        _dev(positions, "positions", torch.int32), _dev(block_tables, "block_tables", torch.int32), block_tables.shape[1], T,
+        num_heads, num_kv_heads, head_dim, value_dim, head_dim if v_cache is None else value_dim, int(v_cache is None), page_size,
+        float(scale), int(window or 0), int(chunk or 0), _opt(slopes, "slopes", torch.float32), _opt(sinks, "sinks", torch.float32),
+        _stream()), "attention_rows")
+
+
+def head_product(a: torch.Tensor, a_offset: int, a_head_stride: int, w: torch.Tensor, out: torch.Tensor, out_offset: int,
+                 out_head_stride: int, tail: int = 0, freq: Optional[torch.Tensor] = None, amplitude: float = 1.0,
+                 positions: Optional[torch.Tensor] = None) -> None:
+    """out[t, out_offset + h * out_head_stride + n] = sum_k w[h, n, k] * a[t, a_offset + h * a_head_stride + k] for
+    every head h of ``w`` [H, N, K]: a matrix per head, applied to that head's slice of a row. ``tail`` > 0: the tail
+    columns behind a head's K inputs are rotated pair by pair by positions[t] * freq[i] (cos and sin times
+    ``amplitude``) and written behind the head's N outputs."""
+    T = a.shape[0]
+    H, N, K = w.shape
+    if a.dim() != 2 or out.dim() != 2 or out.shape[0] != T:
+        raise KernelError("head_product: a and out must be matrices with one row per token")
+    if a_offset + (H - 1) * a_head_stride + K + tail > a.shape[1] or out_offset + (H - 1) * out_head_stride + N + tail > out.shape[1]:
+        raise KernelError("head_product: a head's slice lies outside a row")
+    if tail and (freq is None or positions is None or 2 * freq.numel() != tail):
+        raise KernelError("head_product: a rotated tail needs tail / 2 frequencies and the positions")
+    check(lib().gi_head_product(
+        _dev(a, "a"), dtype_code(a.dtype), a.shape[1], int(a_offset), int(a_head_stride), _dev(w, "w"), dtype_code(w.dtype), N * K,
+        _dev(out, "out"), dtype_code(out.dtype), out.shape[1], int(out_offset), int(out_head_stride), T, H, N, K, int(tail),
+        _opt(freq, "freq", torch.float32), float(amplitude), 0 if positions is None else _dev(positions, "positions", torch.int32),
+        _stream()), "head_product")
+
+
+def grouped_tile_rows() -> int:
+    """Rows per tile of the products that run one matrix per expert."""
+    return int(lib().gi_grouped_tile_rows())
+
+
+def route_tiles(n_tokens: int, top: int, experts: int) -> int:
+    """An upper bound of the tiles that the (token, choice) pairs of a step make once bucketed by expert."""
+    pairs = n_tokens * top
+    tm = grouped_tile_rows()
+    return (pairs + tm - 1) // tm + min(experts, pairs)
+
+
+def route(x: torch.Tensor, w: torch.Tensor, correction: Optional[torch.Tensor], top: int, ids: torch.Tensor,
+          weights: torch.Tensor, sorted_rows: torch.Tensor, tile_group: torch.Tensor, n_tiles: torch.Tensor) -> None:
+    """Per row of ``x`` [T, D]: s = sigmoid(w x) with ``w`` [E, D] 32-bit; the ``top`` experts with the largest
+    s + correction go to ``ids`` [T, top] and their s to ``weights`` [T, top]. The pairs (token, choice) are then
+    bucketed by expert into tiles of grouped_tile_rows() rows: ``sorted_rows`` (pair index or -1), ``tile_group``
+    (a tile's expert), ``n_tiles`` [1]. Two launches."""
+    T, D = x.shape
+    E = w.shape[0]
+    max_tiles = tile_group.numel()
+    if w.shape != (E, D) or ids.shape != (T, top) or weights.shape != (T, top) or (correction is not None and correction.numel() != E):
+        raise KernelError("route: shapes do not agree")
+    if sorted_rows.numel() < max_tiles * grouped_tile_rows() or max_tiles < route_tiles(T, top, E):
+        raise KernelError("route: the buffers of the tiles are too small")
+    check(lib().gi_route(_dev(x, "x"), dtype_code(x.dtype), T, D, _dev(w, "w", torch.float32), _opt(correction, "correction", torch.float32),
+                         E, int(top), _dev(ids, "ids", torch.int32), _dev(weights, "weights", torch.float32),
+                         _dev(sorted_rows, "sorted_rows", torch.int32), _dev(tile_group, "tile_group", torch.int32),
+                         _dev(n_tiles, "n_tiles", torch.int32), max_tiles, _stream()), "route")
+    count_launches(1)
+
+
+def expert_product(a: torch.Tensor, a_div: int, w: torch.Tensor, out: torch.Tensor, sorted_rows: torch.Tensor,
+                   tile_group: torch.Tensor, n_tiles: torch.Tensor, gated: Optional[str] = None) -> None:
+    """out[pair] = W[expert of pair] a[pair // a_div] for the pairs that ``route`` bucketed, ``w`` [E, N, K] (gated:
+    [E, 2N, K], gate rows first, and out = act(gate) * up with ``gated`` one of ACTIVATIONS)."""
+    E, rows, K = w.shape
+    N = rows // 2 if gated else rows
+    if a.dim() != 2 or a.shape[1] != K or out.dim() != 2 or out.shape[1] != N:
+        raise KernelError("expert_product: shapes do not agree")
+    if gated is not None and gated not in ACTIVATIONS:
+        raise KernelError(f"expert_product: unknown activation '{gated}'")
+    check(lib().gi_expert_product(_dev(a, "a"), dtype_code(a.dtype), K, int(a_div), _dev(w, "w"), dtype_code(w.dtype), rows * K, K,
+                                  N * K if gated else 0, int(gated is not None), ACTIVATIONS.get(gated, 0), _dev(out, "out"),
+                                  dtype_code(out.dtype), N, N, K, _dev(tile_group, "tile_group", torch.int32),
+                                  _dev(sorted_rows, "sorted_rows", torch.int32), _dev(n_tiles, "n_tiles", torch.int32),
+                                  tile_group.numel(), _stream()), "expert_product")
+
+
+def route_combine(part: torch.Tensor, weights: torch.Tensor, y: torch.Tensor) -> None:
+    """y[t] += sum_k weights[t, k] * part[t * top + k], in the order of k; all 32-bit."""
+    T, D = y.shape
+    top = weights.shape[1]
+    if part.shape != (T * top, D) or weights.shape[0] != T:
+        raise KernelError("route_combine: shapes do not agree")
+    check(lib().gi_route_combine(_dev(part, "part", torch.float32), _dev(weights, "weights", torch.float32),
+                                 _dev(y, "y", torch.float32), T, D, top, _stream()), "route_combine")
 
 
 def causal_conv(proj: torch.Tensor, offset: int, weight: torch.Tensor, bias: torch.Tensor, state: torch.Tensor,

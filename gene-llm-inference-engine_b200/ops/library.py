@@ -33,7 +33,22 @@ _SIGNATURES = {
     "gi_gated_act": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "gi_norm_rope_store": [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int,
                            c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
-                           c_int, c_int, c_int, c_void_p],
+                           c_int, c_int, c_int, c_int, c_void_p],
+    "gi_add_normed": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_int, c_void_p],
+    "gi_latent_store": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p,
+                        c_float, c_float, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    "gi_attention_rows": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p,
+                          c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int,
+                          c_void_p, c_void_p, c_void_p],
+    "gi_attention_rows_supported": [c_int, c_int],
+    "gi_head_product": [c_void_p, c_int, c_longlong, c_int, c_int, c_void_p, c_int, c_longlong, c_void_p, c_int, c_longlong,
+                        c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_float, c_void_p, c_void_p],
+    "gi_expert_product": [c_void_p, c_int, c_longlong, c_int, c_void_p, c_int, c_longlong, c_int, c_longlong, c_int, c_int,
+                          c_void_p, c_int, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
+    "gi_route": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                 c_void_p, c_int, c_void_p],
+    "gi_route_combine": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    "gi_grouped_tile_rows": [],
     "gi_causal_conv": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_longlong, c_longlong, c_void_p, c_void_p,
                        c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "gi_linear_scan": [c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,

@@ -1,4 +1,4 @@
-from . import attention, block, feed_forward, norm, position, recurrent  # noqa: F401  (registers the parts)
+from . import attention, block, feed_forward, latent, norm, position, recurrent  # noqa: F401  (registers the parts)
 from .model import DecoderModel, LayerRun
 from .registry import (BLOCKS, FEED_FORWARDS, LOGIT_TRANSFORMS, MIXERS, NORMS, POSITION_ENCODINGS, BuildContext, build_part,
                        register_block, register_feed_forward, register_logit_transform, register_mixer, register_norm,

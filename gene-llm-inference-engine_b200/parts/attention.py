@@ -27,7 +27,15 @@ class AttentionMixer:
     normalised per head to unit RMS and multiplied by ``q_norm`` / ``k_norm`` [hd] (shared by the heads)
     before the rotation. ``sink``: the softmax's denominator has one more term, exp(0). ``head_gate``:
     ``w_qkv`` ends with H more rows, and head h's output is multiplied by the sigmoid of its row's product
-    with the input. ``out_scale``: a constant on the mixer's output (applied before the output projection)."""
+    with the input. ``out_scale``: a constant on the mixer's output (applied before the output projection).
+
+    Further options, which run the row-form attention kernel (32-bit arithmetic over shared key tiles):
+    ``value_dim``: value heads of a width of their own (``w_qkv`` then has Hkv * value_dim value rows, ``w_o``
+    H * value_dim columns, and the values have pages of their own). ``qk_norm_weights`` False: the unit-RMS norm of
+    queries and keys has no weights. ``distance_slopes`` [H]: slope_h * (i - j) is taken off the score of key j for the
+    query at i. ``chunk``: position i sees j <= i only inside its own block of ``chunk`` positions counted from 0
+    (pages of earlier blocks are given back). ``sink`` = "learned": the term added to the softmax's denominator is
+    exp(``sink``_h) with a weight per head (``sink`` [H])."""
 
     graph_safe = True      # launches depend only on the step's shape: decode steps may be captured in a CUDA graph
 
@@ -50,33 +58,59 @@ class AttentionMixer:
         if params.get("values", "projected") not in ("projected", "keys"):
             raise ValueError(f"attention: unknown source of values '{params.get('values')}'")
         self.qk_norm_eps = params.get("qk_norm_eps")
+        self.value_dim = int(params.get("value_dim") or self.head_dim)
+        self.chunk = params.get("chunk")
+        self.learned_sink = params.get("sink") == "learned"
+        slopes = params.get("distance_slopes")
+        if slopes is not None and len(slopes) != self.num_heads:
+            raise ValueError("attention: distance_slopes needs one slope per head")
+        self.slopes = None if slopes is None else torch.tensor([float(v) for v in slopes], dtype=torch.float32, device=build.device)
+        # these options are served by the row-form kernel only
+        self.row_form = (self.value_dim != self.head_dim or self.chunk is not None or self.learned_sink or self.slopes is not None)
         self.sink = bool(params.get("sink", False))
         self.head_gate = bool(params.get("head_gate", False))
         self.out_scale = float(params.get("out_scale", 1.0))
         on_device = getattr(self.position, "freq", None) is not None
         self.extended = (self.values_are_keys or self.qk_norm_eps is not None or self.sink or self.head_gate
-                         or self.out_scale != 1.0 or on_device)
+                         or self.out_scale != 1.0 or on_device or self.row_form)
+        if self.row_form:
+            if self.head_gate or self.out_scale != 1.0 or self.values_are_keys:
+                raise ValueError("attention: a gate, an output factor or values taken from the keys cannot be combined with "
+                                 "value_dim, chunk, distance_slopes or a learned sink")
+            if not kernels.attention_rows_supported(self.head_dim, self.value_dim):
+                raise ValueError(f"attention: head size {self.head_dim} with value size {self.value_dim} is not supported")
+        if getattr(self.position, "amplitude", 1.0) != 1.0:
+            raise ValueError("attention: a rotation whose cos and sin are scaled is not served by this mixer")
+        self.sink_weight = None
+        if self.learned_sink:
+            if tuple(weights["sink"].shape) != (self.num_heads,):
+                raise ValueError(f"attention: sink has shape {tuple(weights['sink'].shape)}, expected ({self.num_heads},)")
+            self.sink_weight = weights["sink"].to(device=build.device, dtype=torch.float32).contiguous()
+        elif self.row_form and self.sink:
+            self.sink_weight = torch.zeros(self.num_heads, dtype=torch.float32, device=build.device)      # exp(0) = 1
         if self.extended and getattr(self.position, "cos", None) is not None:
             raise ValueError("attention: with these options the rotation's angles are computed on the device "
                              "(position encoding 'rope_on_device' or 'none')")
         self.q_norm = self.k_norm = None
-        if self.qk_norm_eps is not None:
+        if self.qk_norm_eps is not None and not params.get("qk_norm_weights", True):
+            self.q_norm = self.k_norm = torch.ones(self.head_dim, dtype=torch.float32, device=build.device)
+        elif self.qk_norm_eps is not None:
             for name in ("q_norm", "k_norm"):
                 if tuple(weights[name].shape) != (self.head_dim,):
                     raise ValueError(f"attention: {name} has shape {tuple(weights[name].shape)}, expected ({self.head_dim},)")
                 setattr(self, name, weights[name].to(device=build.device, dtype=torch.float32).contiguous())
-        qkv_rows = (self.num_heads + (1 if self.values_are_keys else 2) * self.num_kv_heads) * self.head_dim + \
-            (self.num_heads if self.head_gate else 0)
+        qkv_rows = (self.num_heads + self.num_kv_heads) * self.head_dim + \
+            (0 if self.values_are_keys else self.num_kv_heads * self.value_dim) + (self.num_heads if self.head_gate else 0)
         if tuple(weights["w_qkv"].shape) != (qkv_rows, self.hidden_size):
             raise ValueError(f"attention: w_qkv has shape {tuple(weights['w_qkv'].shape)}, expected "
                              f"({qkv_rows}, {self.hidden_size})")
-        if tuple(weights["w_o"].shape) != (self.hidden_size, self.num_heads * self.head_dim):
+        if tuple(weights["w_o"].shape) != (self.hidden_size, self.num_heads * self.value_dim):
             raise ValueError(f"attention: w_o has shape {tuple(weights['w_o'].shape)}")
         self.w_qkv = Linear(weights["w_qkv"], build.compute_dtype, build.device, tiles=build.weight_tiles)
         self.w_o = Linear(weights["w_o"], build.compute_dtype, build.device, tiles=build.weight_tiles)
         self.dtype = build.compute_dtype
         # bfloat16 with a head size the tensor-core kernels are built for; else the general kernel
-        self.fast = self.dtype is torch.bfloat16 and kernels.attention_fast_supported(
+        self.fast = self.dtype is torch.bfloat16 and not self.row_form and kernels.attention_fast_supported(
             self.head_dim, self.num_heads, self.num_kv_heads)
         self._prefill_rows = {}
         if self.fast:
@@ -99,7 +133,8 @@ class AttentionMixer:
         return self._prefill_rows[page_size]
 
     def cache_need(self):
-        return CacheNeed(self.num_kv_heads, self.head_dim, self.window)
+        return CacheNeed(self.num_kv_heads, self.head_dim, self.window,
+                         value_dim=None if self.value_dim == self.head_dim else self.value_dim, chunk=self.chunk)
 
     def state_need(self):
         return None
@@ -185,7 +220,14 @@ class AttentionMixer:
         kernels.norm_rope_store(proj, 0, k_off, v_off, self.q_norm, self.k_norm, self.qk_norm_eps or 0.0,
                                 getattr(self.position, "freq", None), self.position.interleaved, ctx.positions,
                                 ctx.row_req, tables, q, k_cache, v_cache, H, Hkv, hd, ctx.page_size,
-                                write_kv=run.writes_cache)
+                                write_kv=run.writes_cache, value_dim=self.value_dim)
+        if self.row_form:
+            att = ctx.scratch("att", (T, H * self.value_dim), self.dtype)
+            kernels.attention_rows(q, k_cache, v_cache, att, ctx.row_req, ctx.positions, tables, H, Hkv, hd, self.value_dim,
+                                   ctx.page_size, self.scale, window=self.window, chunk=self.chunk, slopes=self.slopes,
+                                   sinks=self.sink_weight)
+            self.w_o.forward(att, x, accumulate=True, then=then)
+            return
         att = ctx.scratch("att", (T, H * hd), self.dtype)
         self._attend(ctx, q, k_cache, v_cache, att, tables, sink=self.sink, gate=proj if self.head_gate else None,
                      gate_offset=gate_off, out_scale=self.out_scale)

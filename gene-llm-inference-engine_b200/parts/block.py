@@ -111,6 +111,61 @@ class PostNormBlock:
             carry["post_norm"] = (x.data_ptr(), self.alpha)      # acc = alpha x and xn = x hold for whoever runs next
 
 
+@register_block("output_norm")
+class OutputNormBlock:
+    """x <- x + N1(mixer(x)) and, when the layer has a feed-forward, x <- x + N2(ff(x)): the norm stands on the
+    sublayer's output only, and the sublayers read the stream x itself.
+
+    The stream stays 32-bit. A sublayer reads ``xn`` (x in the compute dtype; x itself on the 32-bit path) and adds
+    its output to ``y``, which is zero when it starts. One kernel adds the normed y to x and, in the same pass,
+    writes the next sublayer's xn and clears y; the next layer of this arrangement finds both ready (``ctx.carry``)."""
+
+    def __init__(self, layer_spec, weights, build):
+        self.mixer_norm = build_part(NORMS, "norm", layer_spec.mixer_norm, sub_weights(weights, "mixer_norm."), build)
+        self.mixer = build_part(MIXERS, "mixer", layer_spec.mixer, sub_weights(weights, "mixer."), build)
+        self.feed_forward = self.feed_forward_norm = None
+        if layer_spec.feed_forward is not None:
+            self.feed_forward_norm = build_part(NORMS, "norm", layer_spec.feed_forward_norm,
+                                                sub_weights(weights, "feed_forward_norm."), build)
+            self.feed_forward = build_part(FEED_FORWARDS, "feed-forward", layer_spec.feed_forward,
+                                           sub_weights(weights, "feed_forward."), build)
+        self.dtype = build.compute_dtype
+
+    def forward(self, ctx, run, x: torch.Tensor) -> None:
+        from ..ops import kernels
+        T = x.shape[0]
+        y = ctx.scratch("output_norm_y", tuple(x.shape), torch.float32)
+        xn = x if self.dtype is torch.float32 else ctx.scratch("normed", tuple(x.shape), self.dtype)
+        carry = getattr(ctx, "carry", None)
+        ready = carry is not None and carry.get("output_norm") == x.data_ptr()
+        cast = None if xn is x else xn
+
+        def mixer_half():
+            if not ready:
+                kernels.scale_cast(x, y, cast, 0.0)          # y = 0, xn = x
+            self.mixer.forward(ctx, run, xn, y)
+            kernels.add_normed(y, self.mixer_norm.weight, x, self.mixer_norm.eps, xn_out=cast, clear_y=True)
+
+        key = _launch_key(ctx, (self.mixer_norm, None), (self.mixer, run))
+        if key is not None:
+            ctx.recorded(self, ("mixer", run, T, ready) + key, mixer_half)
+        else:
+            mixer_half()
+        ctx.tap("attn_out", run.layer, x)
+        if self.feed_forward is not None:
+            def feed_forward_half():
+                self.feed_forward.forward(ctx, xn, y)
+                kernels.add_normed(y, self.feed_forward_norm.weight, x, self.feed_forward_norm.eps, xn_out=cast, clear_y=True)
+            key = _launch_key(ctx, (self.feed_forward_norm, None), (self.feed_forward, None))
+            if key is not None:
+                ctx.recorded(self, ("feed_forward", T) + key, feed_forward_half)
+            else:
+                feed_forward_half()
+        ctx.tap("ffn_out", run.layer, x)
+        if carry is not None:
+            carry["output_norm"] = x.data_ptr()      # y = 0 and xn = x hold for whoever runs next
+
+
 def build_extra(layer_spec, key: str, table, what: str, weights, build):
     """Builds the part that a layer's ``extra`` names ``key`` (for arrangements with more parts than
     the usual four), with the weights under ``<key>.``."""

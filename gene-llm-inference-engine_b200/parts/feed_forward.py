@@ -56,3 +56,61 @@ class SwiGLUFeedForward:
             else:
                 kernels.gated_act(gu, h, self.activation)
         self.w_down.forward(h, x, accumulate=True)
+
+
+@register_feed_forward("routed_experts")
+class RoutedExpertsFeedForward:
+    """A mixture of small gated feed-forwards of which every token uses ``top``: with z = W_r u in 32-bit and
+    s = sigmoid(z), the experts with the largest s_e + ``correction``_e are chosen (the correction steers the choice
+    only), and x += sum over the chosen e of s_e * W_down,e (act(W_gate,e u) * (W_up,e u)); the weights s_e are used
+    as they are, not renormalised.
+
+    Params: ``hidden_size``, ``intermediate_size`` (of one expert), ``experts``, ``top`` and optionally ``activation``
+    ("silu"). Weights: ``router`` [E, hidden], ``correction`` [E], ``w_gate_up`` [E, 2I, hidden] (an expert's gate rows,
+    then its up rows), ``w_down`` [E, hidden, I].
+
+    The step's (token, choice) pairs are bucketed by expert on the device into tiles of a few rows; each tile runs
+    its expert's matrices. The launches depend on the token count only (tiles beyond the step's number leave at once),
+    so the part is recorded into launch programs and CUDA graphs like the dense one."""
+
+    graph_safe = True
+
+    def __init__(self, params, weights, build):
+        self.hidden_size, self.intermediate_size = int(params["hidden_size"]), int(params["intermediate_size"])
+        self.experts, self.top = int(params["experts"]), int(params["top"])
+        self.activation = params.get("activation", "silu")
+        if self.activation not in kernels.ACTIVATIONS:
+            raise ValueError(f"routed experts: unknown activation '{self.activation}'")
+        if not (1 <= self.top <= self.experts):
+            raise ValueError(f"routed experts: top {self.top} must lie between 1 and the {self.experts} experts")
+        E, I, D = self.experts, self.intermediate_size, self.hidden_size
+        for name, shape in (("router", (E, D)), ("correction", (E,)), ("w_gate_up", (E, 2 * I, D)), ("w_down", (E, D, I))):
+            if tuple(weights[name].shape) != shape:
+                raise ValueError(f"routed experts: {name} has shape {tuple(weights[name].shape)}, expected {shape}")
+        dev, dt = build.device, build.compute_dtype
+        self.router = weights["router"].to(device=dev, dtype=torch.float32).contiguous()
+        self.correction = weights["correction"].to(device=dev, dtype=torch.float32).contiguous()
+        self.w_gate_up = weights["w_gate_up"].to(device=dev, dtype=dt).contiguous()
+        self.w_down = weights["w_down"].to(device=dev, dtype=dt).contiguous()
+        self.dtype = dt
+
+    def launch_key(self, ctx):
+        return ()
+
+    def forward(self, ctx, xn: torch.Tensor, x: torch.Tensor) -> None:
+        T = xn.shape[0]
+        E, I, D, top = self.experts, self.intermediate_size, self.hidden_size, self.top
+        most = getattr(ctx, "max_step_tokens", T)
+        tm = kernels.grouped_tile_rows()
+        tiles, most_tiles = kernels.route_tiles(T, top, E), kernels.route_tiles(max(most, T), top, E)
+        ids = ctx.scratch("route_ids", (T, top), torch.int32)
+        weights = ctx.scratch("route_weights", (T, top), torch.float32)
+        sorted_rows = ctx.scratch("route_sorted_rows", (tiles * tm,), torch.int32, capacity=most_tiles * tm)
+        tile_group = ctx.scratch("route_tile_group", (tiles,), torch.int32, capacity=most_tiles)
+        n_tiles = ctx.scratch("route_n_tiles", (1,), torch.int32, capacity=1)
+        kernels.route(xn, self.router, self.correction, top, ids, weights, sorted_rows, tile_group, n_tiles)
+        hidden = ctx.scratch("expert_hidden", (T * top, I), torch.float32, capacity=max(most, T) * top)
+        kernels.expert_product(xn, top, self.w_gate_up, hidden, sorted_rows, tile_group, n_tiles, gated=self.activation)
+        part = ctx.scratch("expert_out", (T * top, D), torch.float32, capacity=max(most, T) * top)
+        kernels.expert_product(hidden, 1, self.w_down, part, sorted_rows, tile_group, n_tiles)
+        kernels.route_combine(part, weights, x)

@@ -52,7 +52,12 @@ class DecoderModel:
         for i, layer_spec in enumerate(spec.layers):
             if layer_spec.block not in BLOCKS:
                 raise KeyError(f"unknown block arrangement '{layer_spec.block}'")
+            if i in spec.shared_layers:
+                self.layers.append(None)        # the parts of another layer, filled in below
+                continue
             self.layers.append(BLOCKS[layer_spec.block](layer_spec, sub_weights(params, f"layers.{i}."), build))
+        for i, j in spec.shared_layers.items():
+            self.layers[i] = self.layers[j]
         self.runs = [LayerRun(e.layer, e.layer if e.cache_of is None else e.cache_of, e.writes_cache)
                      for e in spec.schedule]
         self.final_norm = build_part(NORMS, "norm", spec.final_norm, sub_weights(params, "final_norm."), build)

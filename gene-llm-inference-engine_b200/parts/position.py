@@ -79,7 +79,13 @@ class RotaryOnDevice:
     the 32-bit position by the pair's 32-bit frequency and takes sine and cosine, so no table of
     ``max_position`` rows exists and no position is too far. Params: ``head_dim``, ``theta``, ``pairing``
     ("interleaved" or "half_split"), optional ``rotary_dim`` (< head_dim rotates only the first dims).
-    ``freq`` [rotary_dim / 2] = theta^(-2i / rotary_dim), taken in double and rounded once."""
+    ``freq`` [rotary_dim / 2] = theta^(-2i / rotary_dim), taken in double and rounded once.
+
+    Optional ``ramp_scaling`` {factor, original, fast, slow} stretches the slow pairs for contexts longer than
+    ``original`` positions: with n(t) = rotary_dim ln(original / (2 pi t)) / (2 ln theta) the index of the pair that
+    turns t times within ``original`` positions, lo = max(floor(n(fast)), 0), hi = min(ceil(n(slow)), rotary_dim - 1)
+    and r_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1), pair i turns at f_i (1 - r_i) + f_i r_i / factor, and
+    cos and sin are multiplied by ``amplitude`` = 0.1 ln(factor) + 1 (1 without scaling)."""
 
     applies = "qk_before_store"
     cos = None
@@ -97,4 +103,19 @@ class RotaryOnDevice:
         self.interleaved = pairing == "interleaved"
         i = np.arange(self.rotary_dim // 2, dtype=np.float64)
         freq = np.power(float(params["theta"]), -2.0 * i / self.rotary_dim)
+        self.amplitude = 1.0
+        ramp = params.get("ramp_scaling")
+        if ramp:
+            factor, original = float(ramp["factor"]), float(ramp["original"])
+            if not (factor > 0 and original > 0 and float(ramp["fast"]) > 0 and float(ramp["slow"]) > 0):
+                raise ValueError("rope: the numbers of ramp_scaling must be positive")
+
+            def pair_index(turns: float) -> float:
+                return self.rotary_dim * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(float(params["theta"])))
+
+            lo = max(math.floor(pair_index(float(ramp["fast"]))), 0)
+            hi = min(math.ceil(pair_index(float(ramp["slow"]))), self.rotary_dim - 1)
+            r = np.clip((i - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+            freq = freq / factor * r + freq * (1.0 - r)
+            self.amplitude = 0.1 * math.log(factor) + 1.0
         self.freq = torch.from_numpy(freq.astype(np.float32)).to(build.device).contiguous()

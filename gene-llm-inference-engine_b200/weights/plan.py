@@ -144,6 +144,77 @@ def nipadra_weight_plan(cfg) -> WeightPlan:
     return WeightPlan(rules, [], assemble)
 
 
+def gekupel_weight_plan(cfg) -> WeightPlan:
+    """Tensor names and shapes of a Gekupel checkpoint: ``embed``, ``head``, ``final.norm`` and, for a layer i that has
+    weights of its own, ``l<i>.norm1`` / ``l<i>.norm2``, the mixer's tensors under ``l<i>.mix.`` and the feed-forward's
+    under ``l<i>.mlp.`` (a mixture: ``e<k>.gate`` / ``.up`` / ``.down`` per expert, ``router``, ``correction``). A layer
+    that names another under ``weights_of`` has none. Projections that read the same input become one product: [q; k; v]
+    of the attention, [dq; dkv] of the latent attention, [gate; up] of a feed-forward; the experts' matrices are stacked."""
+    D, V = cfg.width, cfg.vocab
+    rules = [TensorRule("embed", (V, D)), TensorRule("head", (V, D)), TensorRule("final.norm", (D,), "vector")]
+    for i, layer in enumerate(cfg.layers):
+        if layer.weights_of is not None:
+            continue
+        p, m = f"l{i}.", layer.mixer
+        rules.append(TensorRule(p + "norm1", (D,), "vector"))
+        if layer.type == "attention":
+            rules += [TensorRule(p + "mix.q", (m.heads * m.dim, D)), TensorRule(p + "mix.k", (m.kv_heads * m.dim, D)),
+                      TensorRule(p + "mix.v", (m.kv_heads * m.vdim, D)), TensorRule(p + "mix.o", (D, m.heads * m.vdim)),
+                      TensorRule(p + "mix.sink", (m.heads,), "vector", (0.0, 1.0))]
+        else:
+            rules += [TensorRule(p + "mix.dq", (m.q_rank, D)), TensorRule(p + "mix.dq.norm", (m.q_rank,), "vector"),
+                      TensorRule(p + "mix.uq", (m.heads * (m.dim + m.rot_dim), m.q_rank)),
+                      TensorRule(p + "mix.dkv", (m.kv_rank + m.rot_dim, D)), TensorRule(p + "mix.dkv.norm", (m.kv_rank,), "vector"),
+                      TensorRule(p + "mix.uk", (m.heads * m.dim, m.kv_rank)), TensorRule(p + "mix.uv", (m.heads * m.vdim, m.kv_rank)),
+                      TensorRule(p + "mix.o", (D, m.heads * m.vdim))]
+            if m.sink:
+                rules.append(TensorRule(p + "mix.sink", (m.heads,), "vector", (0.0, 1.0)))
+        f = layer.mlp
+        if f is None:
+            continue
+        rules.append(TensorRule(p + "norm2", (D,), "vector"))
+        if f.kind == "dense":
+            rules += [TensorRule(p + "mlp.gate", (f.ff, D)), TensorRule(p + "mlp.up", (f.ff, D)), TensorRule(p + "mlp.down", (D, f.ff))]
+        else:
+            for e in range(f.experts):
+                q = f"{p}mlp.e{e}."
+                rules += [TensorRule(q + "gate", (f.ff, D)), TensorRule(q + "up", (f.ff, D)), TensorRule(q + "down", (D, f.ff))]
+            rules += [TensorRule(p + "mlp.router", (f.experts, D)), TensorRule(p + "mlp.correction", (f.experts,), "vector", (0.0, 0.1))]
+
+    def assemble(t: Dict[str, torch.Tensor]) -> Dict[str, torch.Tensor]:
+        out: Dict[str, torch.Tensor] = {"embedding.weight": t["embed"], "head.weight": t["head"], "final_norm.weight": t["final.norm"]}
+        for i, layer in enumerate(cfg.layers):
+            if layer.weights_of is not None:
+                continue
+            p, q = f"l{i}.", f"layers.{i}."
+            out[q + "mixer_norm.weight"] = t[p + "norm1"]
+            a, b = p + "mix.", q + "mixer."
+            if layer.type == "attention":
+                out[b + "w_qkv"] = _cat([t[a + "q"], t[a + "k"], t[a + "v"]])
+            else:
+                out[b + "w_down"] = _cat([t[a + "dq"], t[a + "dkv"]])
+                out[b + "q_latent_norm"], out[b + "kv_latent_norm"] = t[a + "dq.norm"], t[a + "dkv.norm"]
+                out[b + "w_uq"], out[b + "w_uk"], out[b + "w_uv"] = t[a + "uq"], t[a + "uk"], t[a + "uv"]
+            out[b + "w_o"] = t[a + "o"]
+            if a + "sink" in t:
+                out[b + "sink"] = t[a + "sink"]
+            f = layer.mlp
+            if f is None:
+                continue
+            out[q + "feed_forward_norm.weight"] = t[p + "norm2"]
+            a, b = p + "mlp.", q + "feed_forward."
+            if f.kind == "dense":
+                out[b + "w_gate_up"] = _cat([t[a + "gate"], t[a + "up"]])
+                out[b + "w_down"] = t[a + "down"]
+            else:
+                out[b + "w_gate_up"] = torch.stack([_cat([t[f"{a}e{e}.gate"], t[f"{a}e{e}.up"]]) for e in range(f.experts)])
+                out[b + "w_down"] = torch.stack([t[f"{a}e{e}.down"] for e in range(f.experts)])
+                out[b + "router"], out[b + "correction"] = t[a + "router"], t[a + "correction"]
+        return out
+
+    return WeightPlan(rules, [], assemble)
+
+
 def _cat(parts: List[torch.Tensor]) -> torch.Tensor:
     """Concatenates rows; parts of different stored dtypes are widened to 32-bit first."""
     if len({p.dtype for p in parts}) > 1:
