@@ -6,6 +6,7 @@
                                         (continuous batching / shared prefixes through the scheduler, see run_scenario)
     python bench.py --scenario sizes [--shape ...]   (decode steps at a grid of batch sizes and contexts, see run_sizes)
     python bench.py --scenario nipadra               (the Nipadra design beside Llama at equal layer sizes, see run_nipadra)
+    python bench.py --scenario gekupel               (the Gekupel design beside Llama at equal layer sizes, see run_gekupel)
 
 Prints ONE JSON line. ``value`` is decoded tokens per second at batch 8 and context 8192, timed on
 the device over exactly K decode steps (one step = one token for every request of the batch);
@@ -143,7 +144,7 @@ def prefill_flops(cfg, T):
 def fill_cache(engine, keys, length):
     """Gives each request ``length`` cached positions of random keys and values (setup, untimed):
     decoding reads them exactly as it would read real ones."""
-    for t in engine.group_pages:
+    for t in list(engine.group_pages) + [v for v in getattr(engine, "group_value_pages", []) if v is not None]:
         t.normal_(0.0, 1.0)
     for key in keys:
         rc = engine.open(key)
@@ -583,6 +584,218 @@ def run_nipadra(args):
     return 0
 
 
+# ---------------------------------------------------------------------------------------------- Gekupel beside Llama
+def gekupel_config(width, ff, layers, vocab, heads, head_dim, kv_heads, span):
+    """A Gekupel model with the layer sizes of a Llama shape: the attention layers have Llama's heads, the latent ones
+    half as many heads with a rotated part of half a head and latents of 3/8 (queries) and 1/4 (keys, values) of the
+    width; the mixture has 8 experts of half the dense width of which a token uses 2 (the dense layer's
+    multiply-adds). Layers in turn: latent (scaled rotation, sink) with a dense feed-forward, attention with experts,
+    latent with experts, attention with experts."""
+    lh = max(heads // 2, 1)
+    rot = {"base": 500000.0, "dims": head_dim // 2}
+    lat = {"dim": head_dim, "heads": lh, "kv_rank": width // 4, "mask": {"size": span}, "q_rank": 3 * width // 8, "rot": rot,
+           "rot_dim": head_dim // 2, "scale": (head_dim + head_dim // 2) ** -0.5, "vdim": head_dim}
+    lat2 = dict(lat, rot=dict(rot, scaling={"factor": 4.0, "fast": 32.0, "original": 8192, "slow": 1.0}))
+    att = {"dim": head_dim, "heads": heads, "kv_heads": kv_heads, "mask": {"size": span}, "scale": head_dim ** -0.5, "vdim": head_dim}
+    moe = {"expert": {"ff": ff // 2}, "kind": "moe", "router": {"experts": 8, "top": 2}}
+    kinds = [{"mixer": lat2, "mlp": {"ff": ff, "kind": "dense"}, "type": "latent_attention_2"},
+             {"mixer": att, "mlp": moe, "type": "attention"},
+             {"mixer": lat, "mlp": moe, "type": "latent_attention"},
+             {"mixer": att, "mlp": moe, "type": "attention"}]
+    return {"architecture": "Gekupel", "embedding": {"scale": 1.0}, "layers": [kinds[i % 4] for i in range(layers)],
+            "norm": {"eps": 1e-6}, "vocab": vocab, "width": width}
+
+
+def gekupel_kernel_table(width, heads, kv_heads, head_dim, span, ff, T, pk):
+    """Each kernel of the new design alone, and the like kernel of the Llama path, at the sizes of one layer: a prompt
+    portion of ``T`` tokens of one request and a decode step of 8 requests at a context of ``T``. ``frac`` is the time
+    the kernel's algorithmic bytes (or, where larger, its multiply-adds at the tensor cores' measured rate) need,
+    divided by the time it took; ``frac_of_32bit_issue`` the same against the CUDA cores' 32-bit rate, for kernels
+    whose arithmetic has to stay 32-bit."""
+    import torch
+    from geneinfer_b200.ops import kernels as K
+    dev = torch.device("cuda:0")
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    rows = []
+    props = torch.cuda.get_device_properties(dev)
+    simt_ops = props.multi_processor_count * 128 * 1.965e9
+    bf = torch.bfloat16
+
+    def add(name, like, fn, nbytes, flops=0.0, simt=0.0):
+        ms = time_calls(fn, flush=flush)
+        ideal = max(nbytes / (pk["hbm_gbs"] * 1e9), flops / (pk["bf16_tflops"] * 1e12)) * 1e3
+        row = {"kernel": name, "like": like, "us": round(ms * 1e3, 1), "frac": round(ideal / ms, 3)}
+        if simt:
+            row["frac_of_32bit_issue"] = round(simt / simt_ops * 1e3 / ms, 3)
+        rows.append(row)
+
+    D, page = width, 16
+    lh, rot, kr, qr = max(heads // 2, 1), head_dim // 2, width // 4, 3 * width // 8
+    E, top, I = 8, 2, ff // 2
+    for what, R, n in (("prefill", 1, T), ("decode", 8, 1)):
+        N = R * n
+        i32 = dict(dtype=torch.int32, device=dev)
+        rr = torch.arange(R, **i32).repeat_interleave(n)
+        n_pages = R * ((T + page - 1) // page)
+        tables = torch.arange(n_pages, **i32).view(R, -1)
+        pos = (torch.arange(n, **i32) + (T - n)).repeat(R)
+        x, y = torch.randn(N, D, device=dev), torch.randn(N, D, device=dev)
+        xn = torch.empty(N, D, dtype=bf, device=dev)
+        w = torch.ones(D, device=dev)
+        add(f"add_normed ({what})", "rmsnorm", lambda: K.add_normed(y, w, x, 1e-6, xn_out=xn, clear_y=True), N * D * 18)
+        add(f"rmsnorm, Llama ({what})", "", lambda: K.rmsnorm(x, w, xn, 1e-6), N * D * 6)
+        # latent attention: store, queries through the heads' key matrices, attention over the latent rows, values
+        down = torch.randn(N, qr + kr + rot, device=dev)
+        cq = torch.empty(N, qr, dtype=bf, device=dev)
+        cache = torch.randn(n_pages, 1, page, kr + rot, device=dev).to(bf)
+        freq = torch.rand(rot // 2, device=dev)
+        wq, wc = torch.ones(qr, device=dev), torch.ones(kr, device=dev)
+        add(f"latent_store ({what})", "rope_store", lambda: K.latent_store(down, 0, wq, cq, qr, wc, qr + kr, freq, 1.1, 1e-6, pos, rr,
+                                                                          tables, cache, page), N * ((qr + kr + rot) * 6))
+        q = torch.randn(N, lh * (head_dim + rot), device=dev)
+        wuk = (torch.randn(lh, kr, head_dim, device=dev) * 0.05).to(bf)
+        qa = torch.empty(N, lh * (kr + rot), device=dev)
+        add(f"head_product, queries ({what})", "product", lambda: K.head_product(q, 0, head_dim + rot, wuk, qa, 0, kr + rot, tail=rot,
+                                                                                 freq=freq, amplitude=1.1, positions=pos),
+            lh * kr * head_dim * 2 + N * lh * (head_dim + kr + 2 * rot) * 4, flops=2.0 * N * lh * kr * head_dim,
+            simt=N * lh * kr * head_dim)
+        ol = torch.empty(N, lh * kr, device=dev)
+        seen = sum(min(span, p + 1) for p in range(T - n, T))
+        lat_bytes = R * min(T, span + n) * (kr + rot) * 2 + N * lh * (2 * kr + rot) * 4
+        add(f"attention_rows over the latent, window {span} ({what})", "attention",
+            lambda: K.attention_rows(qa, cache, None, ol, rr, pos, tables, lh, 1, kr + rot, kr, page, 0.1, window=span),
+            lat_bytes, flops=2.0 * R * seen * lh * (2 * kr + rot), simt=R * seen * lh * (2 * kr + rot))
+        wuv = (torch.randn(lh, head_dim, kr, device=dev) * 0.05).to(bf)
+        att = torch.empty(N, lh * head_dim, dtype=bf, device=dev)
+        add(f"head_product, values ({what})", "product", lambda: K.head_product(ol, 0, kr, wuv, att, 0, head_dim),
+            lh * kr * head_dim * 2 + N * lh * (kr * 4 + head_dim * 2), flops=2.0 * N * lh * kr * head_dim, simt=N * lh * kr * head_dim)
+        # attention in blocks with a distance bias and sinks, beside Llama's attention over the same context
+        kc = torch.randn(n_pages, kv_heads, page, head_dim, device=dev).to(bf)
+        vc = torch.randn(n_pages, kv_heads, page, head_dim, device=dev).to(bf)
+        q2 = torch.randn(N, heads * head_dim, device=dev).to(bf)
+        o2 = torch.empty_like(q2)
+        slopes, sinks = torch.rand(heads, device=dev) * 0.1, torch.randn(heads, device=dev)
+        seen_c = sum(p % span + 1 for p in range(T - n, T))
+        add(f"attention_rows in blocks of {span} with bias and sinks ({what})", "attention",
+            lambda: K.attention_rows(q2, kc, vc, o2, rr, pos, tables, heads, kv_heads, head_dim, head_dim, page, head_dim ** -0.5,
+                                     chunk=span, slopes=slopes, sinks=sinks),
+            R * min(T, span) * kv_heads * head_dim * 4 + N * heads * head_dim * 4, flops=4.0 * R * seen_c * heads * head_dim,
+            simt=2.0 * R * seen_c * heads * head_dim)
+        rows_dec = torch.arange(R, **i32)
+        per_tile = 128 // (heads // kv_heads)
+        work = torch.tensor([(t, min(per_tile, n - t), 0) for t in range(0, n, per_tile)][::-1], **i32)
+        chunk = K.attention_chunk_keys()
+        n_chunks = (T + chunk - 1) // chunk
+        part_o = torch.empty(R, heads * n_chunks * head_dim, device=dev)
+        part_ml = torch.empty(R, heads * n_chunks * 2, device=dev)
+
+        def llama_attention():
+            if n == 1:
+                K.attention_decode(q2, kc, vc, o2, rows_dec, rr, pos, tables, heads, kv_heads, head_dim, page, head_dim ** -0.5,
+                                   span, part_o, part_ml, n_chunks, n_chunks)
+            else:
+                K.attention_prefill_tc(q2, kc, vc, o2, work, pos, tables, heads, kv_heads, head_dim, page, head_dim ** -0.5, span)
+
+        seen_w = sum(min(span, p + 1) for p in range(T - n, T))
+        add(f"attention, Llama kernels, window {span} ({what})", "", llama_attention,
+            R * min(T, span + n) * kv_heads * head_dim * 4 + N * heads * head_dim * 4, flops=4.0 * R * seen_w * heads * head_dim)
+        # routed experts beside the dense products of the same multiply-adds
+        router, corr = torch.randn(E, D, device=dev) * 0.1, torch.zeros(E, device=dev)
+        wgu = (torch.randn(E, 2 * I, D, device=dev) * 0.02).to(bf)
+        wd = (torch.randn(E, D, I, device=dev) * 0.02).to(bf)
+        xb = torch.randn(N, D, device=dev).to(bf)
+        ids, wts = torch.empty(N, top, **i32), torch.empty(N, top, device=dev)
+        cnt = torch.empty(1, **i32)
+        tc = N * top >= 256
+        tm = K.TC_TILE_ROWS if tc else K.grouped_tile_rows()
+        tiles = K.route_tiles(N, top, E, tm)
+        srt, grp, prow = torch.empty(tiles * tm, **i32), torch.empty(tiles, **i32), torch.empty(N * top, **i32)
+        add(f"route + bucket ({what})", "", lambda: K.route(xb, router, corr, top, ids, wts, srt, grp, cnt, tile_rows=tm, pair_row=prow),
+            N * D * 2 + E * D * 4)
+        used = int(cnt.item())
+        experts_hit = len(set(ids.view(-1).tolist()))
+        if tc:
+            rows_x = torch.empty(tiles * tm, D, dtype=bf, device=dev)
+            hid = torch.empty(tiles * tm, I, dtype=bf, device=dev)
+            part = torch.empty(tiles * tm, D, device=dev)
+            add(f"gather_rows ({what})", "", lambda: K.gather_rows(xb, top, srt, cnt, tm, rows_x), used * tm * D * 4)
+            add(f"experts [gate; up] on the tensor cores, {used} tiles ({what})", "product",
+                lambda: K.expert_product_tc(rows_x, wgu, hid, grp, cnt, gated="silu"),
+                experts_hit * 2 * I * D * 2 + used * tm * (D + I) * 2, flops=2.0 * N * top * 2 * I * D)
+            add(f"experts down on the tensor cores ({what})", "product", lambda: K.expert_product_tc(hid, wd, part, grp, cnt),
+                experts_hit * I * D * 2 + used * tm * (I * 2 + D * 4), flops=2.0 * N * top * I * D)
+            yy = torch.zeros(N, D, device=dev)
+            add(f"route_combine ({what})", "", lambda: K.route_combine(part, wts, yy, pair_row=prow), N * D * (8 + 4 * top))
+        else:
+            hid = torch.empty(N * top, I, device=dev)
+            part = torch.empty(N * top, D, device=dev)
+            add(f"experts [gate; up], tiles of 16 rows, {experts_hit} experts hit ({what})", "product",
+                lambda: K.expert_product(xb, top, wgu, hid, srt, grp, cnt, gated="silu"), experts_hit * 2 * I * D * 2,
+                simt=used * 16 * 2 * I * D)
+            add(f"experts down, tiles of 16 rows ({what})", "product", lambda: K.expert_product(hid, 1, wd, part, srt, grp, cnt),
+                experts_hit * I * D * 2, simt=used * 16 * I * D)
+        # the dense products of a Llama layer with as many multiply-adds per token (2 experts of ff / 2 = one dense ff)
+        wg = (torch.randn(2 * ff, D, device=dev) * 0.02).to(bf)
+        wdn = (torch.randn(D, ff, device=dev) * 0.02).to(bf)
+        gu = torch.empty(N, 2 * ff, device=dev)
+        hd_ = torch.empty(N, ff, dtype=bf, device=dev)
+        out = torch.zeros(N, D, device=dev)
+        if K.gemm_swiglu_supported(N, ff, D):
+            add(f"[gate; up] product with activation, Llama ({what})", "", lambda: K.gemm_swiglu(xb, wg, hd_), 2 * ff * D * 2 + N * (D + ff) * 2,
+                flops=2.0 * N * 2 * ff * D)
+        else:
+            wgt = K.tile_weight(wg)
+            add(f"[gate; up] product, Llama ({what})", "", lambda: K.gemm_tc(xb, wg, gu, w_tiles=wgt), 2 * ff * D * 2, flops=2.0 * N * 2 * ff * D)
+        wdt = K.tile_weight(wdn)
+        add(f"down product, Llama ({what})", "", lambda: K.gemm_tc(hd_, wdn, out, True, w_tiles=wdt), ff * D * 2 + N * (ff * 2 + D * 8),
+            flops=2.0 * N * ff * D)
+        del wg, wdn, wgu, wd
+    return rows
+
+
+def run_gekupel(args):
+    """Prefill (one 2,048-token prompt in one step) and decode (batch 8 at context 2,048) throughput of Gekupel models
+    whose layers have the sizes of the Llama-3.2-1B and Llama-3.1-8B shapes (four layers each, random bf16 weights),
+    beside Llama models of the same sizes; then every kernel of the new design alone beside the like kernel of the
+    Llama path. Prints one JSON line."""
+    import torch
+    from geneinfer_b200 import Engine
+    from geneinfer_b200.weights import write_random_model
+    pk = peaks()
+    layers = args.layers or 4
+    context, batch, T = 2048, 8, PREFILL_TOKENS
+    models = []
+    for name, base in (("1b", LLAMA_1B), ("8b", LLAMA_8B)):
+        llama = dict(base, num_hidden_layers=layers, tie_word_embeddings=True)
+        gek = gekupel_config(base["hidden_size"], base["intermediate_size"], layers, base["vocab_size"], base["num_attention_heads"],
+                             base["head_dim"], base["num_key_value_heads"], 1024)
+        for arch, cfg in (("Llama", llama), ("Gekupel", gek)):
+            if arch == "Llama":
+                folder = model_folder(cfg)
+            else:
+                folder = os.path.join(tempfile.gettempdir(), f"geneinfer_bench_gekupel_{name}_{layers}_{os.getuid()}")
+                if not os.path.isfile(os.path.join(folder, "done")):
+                    write_random_model(cfg, 1, folder, "bfloat16", std=0.02)
+                    open(os.path.join(folder, "done"), "w").close()
+            llm = Engine(folder, dtype="bfloat16", max_seq_len=context, page_size=PAGE, kv_pages=batch * (context // PAGE),
+                         max_running=batch, step_tokens=T, prefix_cache=False)
+            vocab = base["vocab_size"]
+            ms_prefill = time_prefill(llm.steps, T, 2, vocab)
+            ms_decode, _ = time_decode_device(llm.steps, batch, context, args.steps, args.warmup, vocab)
+            llm.steps.check_status()
+            models.append({"model": f"{arch} at the {SHAPES[name][0]} layer sizes, {layers} layers",
+                           "prefill_2048_tok_s": round(T / ms_prefill * 1e3, 1), "prefill_ms": round(ms_prefill, 3),
+                           "decode_b8_ctx2048_tok_s": round(batch / ms_decode * 1e3, 1), "decode_ms_per_step": round(ms_decode, 4),
+                           "weight_gb": round(llm.model.weight_bytes() / 1e9, 3)})
+            del llm
+            torch.cuda.empty_cache()
+    table = gekupel_kernel_table(2048, 32, 8, 64, 1024, 8192, T, pk)
+    print(json.dumps({"metric": "Gekupel beside Llama at equal layer sizes (random bf16 weights)", "impl": "ours", "n_gpus": 1,
+                      "dtype": "bf16", "steps": args.steps, "warmup": args.warmup, "peaks": pk["source"],
+                      "peak_gb_s": pk["hbm_gbs"], "peak_tflops": pk["bf16_tflops"], "models": models, "kernels": table}))
+    return 0
+
+
 def run_scenario(args):
     """Two workloads through the entry point, beside the default run: ``mixed`` (32 requests with
     prompts of 128 to 4096 random ids and 256 generated tokens each, admitted together, prompts cut
@@ -793,7 +1006,7 @@ def main():
     ap.add_argument("--shape", choices=sorted(SHAPES), default="1b", help="layer sizes (the default is the baseline's third configuration)")
     ap.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16",
                     help="precision of a --scenario run (float32: the requests run alone must give identical tokens)")
-    ap.add_argument("--scenario", choices=["mixed", "prefix", "sizes", "nipadra"], default="",
+    ap.add_argument("--scenario", choices=["mixed", "prefix", "sizes", "nipadra", "gekupel"], default="",
                     help="a workload through the scheduler (mixed, prefix) or decode steps at a grid of sizes, instead of the default run")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -806,6 +1019,8 @@ def main():
         return run_sizes(args)
     if args.scenario == "nipadra":
         return run_nipadra(args)
+    if args.scenario == "gekupel":
+        return run_gekupel(args)
     if args.scenario:
         return run_scenario(args)
     return run_ours(args)

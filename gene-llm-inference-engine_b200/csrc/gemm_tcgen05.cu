@@ -933,6 +933,11 @@ struct TcPersistentParams {
     int kb_per_split;            //   stored split_rows rows further down in the output (a workspace; the ranges are
     int split_rows;              //   added up, in order, by reduce_splits_kernel): few tiles still fill the GPU
     RopeStoreParams rope;        // epilogue kEpiRopeStore
+    // a matrix per group of rows (one expert's tokens): tile i of 128 tokens multiplies rows tile_group[i] * group_rows ..
+    // of the stacked weights; only the first *tiles_used tiles of tokens exist (both written by an earlier kernel)
+    const int* tile_group;
+    const int* tiles_used;
+    int group_rows;
 };
 
 constexpr int kPersistentThreads = 64 + 2 * 128;     // producer warp, MMA warp, two epilogue groups of four warps
@@ -959,12 +964,13 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __gri
     // 256-row tile of tokens and fetches rows r BLOCK_Q/2 .. of the weights' tile; p.tiles_p counts 256-row tiles.
     const uint32_t rank = PAIR ? cluster_ctarank() : 0u;
     const int worker = PAIR ? blockIdx.x / 2 : blockIdx.x, n_workers = PAIR ? gridDim.x / 2 : gridDim.x;
-    const int out_tiles = p.tiles_p * p.tiles_q;
-    const int n_tiles = out_tiles * p.splits;
+    int tiles_p = p.tiles_p;                 // (with a matrix per group: known only after the wait for earlier kernels)
+    int out_tiles = tiles_p * p.tiles_q;
+    int n_tiles = out_tiles * p.splits;
     // work item t: output tile t % out_tiles, range t / out_tiles of K
     auto kb_first = [&](int t) { return (t / out_tiles) * p.kb_per_split; };
     auto kb_count = [&](int t) { return min(total_kb, kb_first(t) + p.kb_per_split) - kb_first(t); };
-    auto tile_p_of = [&](int t) { return PAIR ? 2 * ((t % out_tiles) % p.tiles_p) + static_cast<int>(rank) : (t % out_tiles) % p.tiles_p; };
+    auto tile_p_of = [&](int t) { return PAIR ? 2 * ((t % out_tiles) % tiles_p) + static_cast<int>(rank) : (t % out_tiles) % tiles_p; };
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
@@ -990,6 +996,11 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __gri
     if (PAIR) cluster_sync_all();    // both CTAs' barriers exist before either signals the other's
     grid_dependency_wait();          // everything below reads what earlier kernels wrote
     if (threadIdx.x == 0) timeline_record(kTl, 1);
+    if (!PAIR && p.tile_group != nullptr) {
+        tiles_p = min(*p.tiles_used, p.tiles_p);
+        out_tiles = tiles_p * p.tiles_q;
+        n_tiles = out_tiles * p.splits;
+    }
     // the first CTA's barriers as the other CTA addresses them: "stage full" counts both CTAs' bytes there, and
     // "accumulator empty" both CTAs' epilogue threads
     auto leader_bar = [&](int i) { return PAIR ? cluster_map(smem_u32(&bars[i]), 0u) : smem_u32(&bars[i]); };
@@ -1002,8 +1013,9 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __gri
         if (lane == 0) {
             int it = 0, issued_ok = 1;
             for (int t = worker; t < n_tiles && issued_ok; t += n_workers) {
-                const int tile_p = tile_p_of(t), tile_q = (t % out_tiles) / p.tiles_p;
+                const int tile_p = tile_p_of(t), tile_q = (t % out_tiles) / tiles_p;
                 const int kb0 = kb_first(t), n_kb = kb_count(t);
+                const int group_row = (!PAIR && p.tile_group != nullptr) ? p.tile_group[tile_p] * p.group_rows : 0;
                 for (int kb = 0; kb < n_kb; ++kb, ++it) {
                     const int s = it % kStages;
                     if (!mbar_wait(smem_u32(&bars[kStages + s]), ((it / kStages) & 1) ^ 1, abort_flag)) {
@@ -1027,11 +1039,11 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __gri
                         mbar_expect_tx(full, Cfg::kStageBytes);
                         tma_load_2d(smem_u32(stage), &map_p, k0, tile_p * kBlockP, full);
                         if (EPI == kEpiSwiGLU) {
-                            const int n0 = tile_q * (BLOCK_Q / 2);
+                            const int n0 = group_row + tile_q * (BLOCK_Q / 2);
                             tma_load_2d(smem_u32(stage + Cfg::kStageBytesP), &map_q, k0, n0, full);
                             tma_load_2d(smem_u32(stage + Cfg::kStageBytesP + Cfg::kStageBytesQ / 2), &map_q, k0, p.up_row_offset + n0, full);
                         } else {
-                            tma_load_2d(smem_u32(stage + Cfg::kStageBytesP), &map_q, k0, tile_q * BLOCK_Q, full);
+                            tma_load_2d(smem_u32(stage + Cfg::kStageBytesP), &map_q, k0, group_row + tile_q * BLOCK_Q, full);
                         }
                     }
                 }
@@ -1105,7 +1117,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __gri
         int j = 0;
         bool ok = true;
         for (int t = worker; t < n_tiles; t += n_workers, ++j) {
-            const int tile_p = tile_p_of(t), tile_q = (t % out_tiles) / p.tiles_p;
+            const int tile_p = tile_p_of(t), tile_q = (t % out_tiles) / tiles_p;
             const int out_row = tile_p * kBlockP + (t / out_tiles) * p.split_rows;
             const int buf = j & 1;
             // Rotation and store: the token's position, its page row and the first cos/sin values are
@@ -1781,6 +1793,52 @@ static int gi_gemm_tc_persistent_impl(const void* A, const void* W, void* C, int
     return finish(launch_persistent<128, kEpiStoreF32>(mp, mq, mc, p, st));
 }
 
+// A matrix per group of rows: A [M, K] holds tiles of 128 rows each of which belongs to one group (an expert's tokens,
+// padded to whole tiles), W [groups * rows, K] the groups' matrices one after the other (rows = N, or 2 N = [gate; up]
+// with epilogue 2), tile_group[i] the group of tile i and *tiles_used how many tiles exist (device memory, written by
+// an earlier kernel). C [M, N] in the rows' order; epilogue 0 stores 32-bit, 2 stores act(gate) * up as bfloat16.
+static int gi_gemm_tc_grouped_impl(const void* A, const void* W, void* C, int epilogue, int M, int N, int K, int groups,
+                                  const int* tile_group, const int* tiles_used, void* status, void* stream) {
+    if (M == 0 || N == 0) return 0;
+    GI_REQUIRE(M > 0 && N > 0 && K > 0 && groups > 0, "gemm_tc grouped: sizes must be positive (M=%d, N=%d, K=%d)", M, N, K);
+    GI_REQUIRE(M % kBlockP == 0, "gemm_tc grouped: %d rows are not whole tiles of %d", M, kBlockP);
+    GI_REQUIRE(K % 8 == 0, "gemm_tc grouped: K=%d must be a multiple of 8 (16-byte rows for TMA)", K);
+    const int gate_act = epilogue >> 8;
+    epilogue &= 0xff;
+    GI_REQUIRE((epilogue == kEpiStoreF32 || epilogue == kEpiSwiGLU) && gate_act >= 0 && gate_act <= 2,
+               "gemm_tc grouped: unknown epilogue %d (activation %d)", epilogue, gate_act);
+    const bool bf16_out = epilogue == kEpiSwiGLU;
+    GI_REQUIRE((static_cast<long long>(N) * (bf16_out ? 2 : 4)) % 16 == 0, "gemm_tc grouped: output rows of %d values are not a multiple of 16 bytes", N);
+    GI_REQUIRE((reinterpret_cast<uintptr_t>(A) % 16 == 0) && (reinterpret_cast<uintptr_t>(W) % 16 == 0) &&
+               (reinterpret_cast<uintptr_t>(C) % 16 == 0), "gemm_tc grouped: operands must be 16-byte aligned");
+    GI_REQUIRE(status != nullptr && tile_group != nullptr && tiles_used != nullptr, "gemm_tc grouped: status word and tile lists are required");
+    const int block_q = (bf16_out ? N >= 128 : N >= 256) ? 256 : 128;
+    TcPersistentParams p = {};
+    p.rows_p = M; p.rows_q = N; p.K = K;
+    p.tiles_p = M / kBlockP;
+    p.up_row_offset = N;
+    p.gate_act = gate_act;
+    p.status = static_cast<int*>(status);
+    p.splits = 1; p.kb_per_split = (K + kBlockK - 1) / kBlockK; p.split_rows = 0;
+    p.tile_group = tile_group; p.tiles_used = tiles_used; p.group_rows = bf16_out ? 2 * N : N;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    CUtensorMap mp, mq, mc;
+    if (make_map(&mp, A, M, K, K, kBlockP)) return 1;
+    if (make_out_map(&mc, C, M, N, N, bf16_out)) return 1;
+    const long long w_rows = static_cast<long long>(groups) * p.group_rows;
+    GI_REQUIRE(w_rows <= 2147483647LL, "gemm_tc grouped: too many weight rows");
+    if (bf16_out) {
+        p.tiles_q = (N + block_q / 2 - 1) / (block_q / 2);
+        if (make_map(&mq, W, static_cast<int>(w_rows), K, K, block_q / 2)) return 1;
+        if (block_q == 256) return launch_persistent<256, kEpiSwiGLU>(mp, mq, mc, p, st);
+        return launch_persistent<128, kEpiSwiGLU>(mp, mq, mc, p, st);
+    }
+    p.tiles_q = (N + block_q - 1) / block_q;
+    if (make_map(&mq, W, static_cast<int>(w_rows), K, K, block_q)) return 1;
+    if (block_q == 256) return launch_persistent<256, kEpiStoreF32>(mp, mq, mc, p, st);
+    return launch_persistent<128, kEpiStoreF32>(mp, mq, mc, p, st);
+}
+
 // The [q; k; v] product of many tokens with rotation and page store in its epilogue (RopeStoreParams):
 // A [M, K] bfloat16 activations, W [(H + 2 Hkv) * hd, K]; nothing else is written. Head sizes 32, 64, 128
 // with the whole head rotated (rot_half = hd / 2) in the half-split pairing, or no rotation at all.
@@ -1846,6 +1904,10 @@ extern "C" int gi_gemm_tc_rope(const void* A, const void* W, int M, int K, long 
 
 extern "C" int gi_gemm_tc_persistent(const void* A, const void* W, void* C, int epilogue, int M, int N, int K, long long lda, long long ldw, long long ldc, int block_q, void* status, int splits, void* workspace, long long workspace_floats, int pair, void* stream) {
     return gi::dispatch(gi_gemm_tc_persistent_impl, A, W, C, epilogue, M, N, K, lda, ldw, ldc, block_q, status, splits, workspace, workspace_floats, pair, stream);
+}
+
+extern "C" int gi_gemm_tc_grouped(const void* A, const void* W, void* C, int epilogue, int M, int N, int K, int groups, const int* tile_group, const int* tiles_used, void* status, void* stream) {
+    return gi::dispatch(gi_gemm_tc_grouped_impl, A, W, C, epilogue, M, N, K, groups, tile_group, tiles_used, status, stream);
 }
 
 extern "C" int gi_gemm_tc_persistent_rope(const void* A, const void* W, int M, int K, long long lda, long long ldw, const int* positions, const int* row_req, const int* block_tables, int table_stride, const float* cos_t, const float* sin_t, int rot_half, int interleaved, void* q_out, void* k_cache, void* v_cache, int H, int Hkv, int hd, int page_size, int write_kv, void* status, int pair, void* stream) {

@@ -10,8 +10,10 @@
 //              sorted_rows[16 i ..] (-1: none); the input row is pair / a_div, the output row the pair;
 //              gated: out = act(W_gate a) * (W_up a) with W[g] = [gate rows; up rows]
 //   route             per token: z = W_r x in 32-bit, s = sigmoid(z), the ``top`` experts by s + correction, weights s
-//   route_align       buckets the pairs by expert into tiles of 16 rows (padding with -1), one block
-//   route_combine     y[t] += sum_k weight[t, k] * part[t * top + k] in the order of k
+//   route_align       buckets the pairs by expert into tiles of 16 rows (padding with -1), one block; for many rows
+//                     into tiles of 128, the token tiles of the tensor-core product that takes a matrix per tile
+//   gather_rows       a[r] = x[sorted_rows[r] / top] (zeros for padding): the rows in the tiles' order
+//   route_combine     y[t] += sum_k weight[t, k] * part[row of pair t * top + k] in the order of k
 //
 // Products run on the CUDA cores with 32-bit fused multiply-adds in the order of k: the true 32-bit path, products of
 // few rows (decoding, where the expert weights stream once), and the bfloat16 path's fallback. An output element is
@@ -190,20 +192,20 @@ route_kernel(const TX* __restrict__ x, int D, const float* __restrict__ w, const
 // One block: counts per expert, then tiles of 16 rows per expert in expert order.
 __global__ void __launch_bounds__(1024)
 route_align_kernel(const int* __restrict__ ids, int n_pairs, int E, int* __restrict__ sorted_rows, int* __restrict__ tile_group,
-                   int* __restrict__ n_tiles, int max_tiles) {
+                   int* __restrict__ n_tiles, int max_tiles, int tile_rows, int* __restrict__ pair_row) {
     pdl_prologue();
     __shared__ int s_count[kRouteMaxExperts], s_start[kRouteMaxExperts];
     const int tid = threadIdx.x;
     for (int e = tid; e < E; e += 1024) s_count[e] = 0;
-    for (int i = tid; i < max_tiles * kGpTM; i += 1024) sorted_rows[i] = -1;
+    for (int i = tid; i < max_tiles * tile_rows; i += 1024) sorted_rows[i] = -1;
     __syncthreads();
     for (int i = tid; i < n_pairs; i += 1024) atomicAdd(&s_count[ids[i]], 1);
     __syncthreads();
     if (tid == 0) {
         int tiles = 0;
         for (int e = 0; e < E; ++e) {
-            s_start[e] = tiles * kGpTM;
-            const int n = (s_count[e] + kGpTM - 1) / kGpTM;
+            s_start[e] = tiles * tile_rows;
+            const int n = (s_count[e] + tile_rows - 1) / tile_rows;
             for (int i = 0; i < n; ++i) tile_group[tiles + i] = e;
             tiles += n;
         }
@@ -212,19 +214,47 @@ route_align_kernel(const int* __restrict__ ids, int n_pairs, int E, int* __restr
     __syncthreads();
     // a pair takes the next free row of its expert (which row does not matter: an output element is computed from
     // its own row alone, in the same order of operations in every row of a tile)
-    for (int i = tid; i < n_pairs; i += 1024) sorted_rows[atomicAdd(&s_start[ids[i]], 1)] = i;
+    for (int i = tid; i < n_pairs; i += 1024) {
+        const int row = atomicAdd(&s_start[ids[i]], 1);
+        sorted_rows[row] = i;
+        if (pair_row) pair_row[i] = row;
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+gather_rows_kernel(const T* __restrict__ x, int D, int a_div, const int* __restrict__ sorted_rows, const int* __restrict__ n_tiles,
+                   int tile_rows, T* __restrict__ out) {
+    pdl_prologue();
+    const int r = blockIdx.x;
+    if (r >= *n_tiles * tile_rows) return;
+    const int pair = sorted_rows[r];
+    T* dst = out + static_cast<size_t>(r) * D;
+    if (pair < 0) {
+        for (int d = threadIdx.x; d < D; d += 256) dst[d] = from_float<T>(0.f);
+        return;
+    }
+    const T* src = x + static_cast<size_t>(pair / a_div) * D;
+    if (D % 8 == 0 && sizeof(T) == 2) {
+        for (int d = threadIdx.x; d < D / 8; d += 256) reinterpret_cast<uint4*>(dst)[d] = reinterpret_cast<const uint4*>(src)[d];
+    } else {
+        for (int d = threadIdx.x; d < D; d += 256) dst[d] = src[d];
+    }
 }
 
 __global__ void __launch_bounds__(256)
-route_combine_kernel(const float* __restrict__ part, const float* __restrict__ weights, float* __restrict__ y, int D, int top,
-                     size_t total) {
+route_combine_kernel(const float* __restrict__ part, const float* __restrict__ weights, const int* __restrict__ pair_row,
+                     float* __restrict__ y, int D, int top, size_t total) {
     pdl_prologue();
     const size_t i = static_cast<size_t>(blockIdx.x) * 256 + threadIdx.x;
     if (i >= total) return;
     const size_t t = i / D;
     const int d = static_cast<int>(i % D);
     float v = y[i];
-    for (int k = 0; k < top; ++k) v = fmaf(weights[t * top + k], part[(t * top + k) * D + d], v);
+    for (int k = 0; k < top; ++k) {
+        const size_t row = pair_row ? static_cast<size_t>(pair_row[t * top + k]) : t * top + k;
+        v = fmaf(weights[t * top + k], part[row * D + d], v);
+    }
     y[i] = v;
 }
 
@@ -282,13 +312,15 @@ static int gi_expert_product_impl(const void* a, int a_dtype, long long lda, int
 }
 
 static int gi_route_impl(const void* x, int x_dtype, int T, int D, const float* w, const float* correction, int E, int top,
-                         int* ids, float* weights, int* sorted_rows, int* tile_group, int* n_tiles, int max_tiles, void* stream) {
+                         int* ids, float* weights, int* sorted_rows, int* tile_group, int* n_tiles, int max_tiles, int tile_rows,
+                         int* pair_row, void* stream) {
     if (T == 0) return 0;
     GI_REQUIRE(T > 0 && D > 0 && E > 0 && top > 0 && top <= E, "route: sizes must be positive and top at most the experts");
     GI_REQUIRE(E <= kRouteMaxExperts, "route: %d experts exceed %d", E, kRouteMaxExperts);
     GI_REQUIRE(static_cast<size_t>(D) * 4 <= 160 * 1024, "route: a row of %d values does not fit shared memory", D);
     const long long pairs = static_cast<long long>(T) * top;
-    GI_REQUIRE(max_tiles >= (pairs + kGpTM - 1) / kGpTM + std::min<long long>(E, pairs) - 1, "route: room for %d tiles is too little", max_tiles);
+    GI_REQUIRE(tile_rows > 0, "route: tiles must have rows");
+    GI_REQUIRE(max_tiles >= (pairs + tile_rows - 1) / tile_rows + std::min<long long>(E, pairs) - 1, "route: room for %d tiles is too little", max_tiles);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const size_t smem = static_cast<size_t>(D) * 4;
     if (x_dtype == kF32) {
@@ -301,16 +333,32 @@ static int gi_route_impl(const void* x, int x_dtype, int T, int D, const float* 
         GI_REQUIRE(false, "route: unsupported dtype code %d", x_dtype);
     }
     if (check_launch("route")) return 1;
-    launch_kernel(route_align_kernel, dim3(1), dim3(1024), 0, st, static_cast<const int*>(ids), static_cast<int>(pairs), E, sorted_rows, tile_group, n_tiles, max_tiles);
+    launch_kernel(route_align_kernel, dim3(1), dim3(1024), 0, st, static_cast<const int*>(ids), static_cast<int>(pairs), E, sorted_rows, tile_group, n_tiles, max_tiles, tile_rows, pair_row);
     return check_launch("route_align");
 }
 
-static int gi_route_combine_impl(const float* part, const float* weights, float* y, int T, int D, int top, void* stream) {
+static int gi_gather_rows_impl(const void* x, int dtype, int D, int a_div, const int* sorted_rows, const int* n_tiles, int tile_rows,
+                               int max_rows, void* out, void* stream) {
+    if (max_rows == 0) return 0;
+    GI_REQUIRE(max_rows > 0 && D > 0 && a_div > 0 && tile_rows > 0, "gather_rows: sizes must be positive");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (dtype == kBF16)
+        launch_kernel((gather_rows_kernel<__nv_bfloat16>), dim3(max_rows), dim3(256), 0, st, static_cast<const __nv_bfloat16*>(x), D, a_div,
+                      sorted_rows, n_tiles, tile_rows, static_cast<__nv_bfloat16*>(out));
+    else if (dtype == kF32)
+        launch_kernel((gather_rows_kernel<float>), dim3(max_rows), dim3(256), 0, st, static_cast<const float*>(x), D, a_div, sorted_rows,
+                      n_tiles, tile_rows, static_cast<float*>(out));
+    else
+        GI_REQUIRE(false, "gather_rows: unsupported dtype code %d", dtype);
+    return check_launch("gather_rows");
+}
+
+static int gi_route_combine_impl(const float* part, const float* weights, const int* pair_row, float* y, int T, int D, int top, void* stream) {
     if (T == 0) return 0;
     GI_REQUIRE(T > 0 && D > 0 && top > 0, "route_combine: sizes must be positive");
     const size_t total = static_cast<size_t>(T) * D;
     launch_kernel(route_combine_kernel, dim3(static_cast<unsigned>((total + 255) / 256)), dim3(256), 0, static_cast<cudaStream_t>(stream),
-                  part, weights, y, D, top, total);
+                  part, weights, pair_row, y, D, top, total);
     return check_launch("route_combine");
 }
 
@@ -329,11 +377,17 @@ extern "C" int gi_expert_product(const void* a, int a_dtype, long long lda, int 
 }
 
 extern "C" int gi_route(const void* x, int x_dtype, int T, int D, const float* w, const float* correction, int E, int top, int* ids,
-                        float* weights, int* sorted_rows, int* tile_group, int* n_tiles, int max_tiles, void* stream) {
+                        float* weights, int* sorted_rows, int* tile_group, int* n_tiles, int max_tiles, int tile_rows, int* pair_row,
+                        void* stream) {
     return gi::dispatch(gi_route_impl, x, x_dtype, T, D, w, correction, E, top, ids, weights, sorted_rows, tile_group, n_tiles,
-                        max_tiles, stream);
+                        max_tiles, tile_rows, pair_row, stream);
 }
 
-extern "C" int gi_route_combine(const float* part, const float* weights, float* y, int T, int D, int top, void* stream) {
-    return gi::dispatch(gi_route_combine_impl, part, weights, y, T, D, top, stream);
+extern "C" int gi_gather_rows(const void* x, int dtype, int D, int a_div, const int* sorted_rows, const int* n_tiles, int tile_rows,
+                              int max_rows, void* out, void* stream) {
+    return gi::dispatch(gi_gather_rows_impl, x, dtype, D, a_div, sorted_rows, n_tiles, tile_rows, max_rows, out, stream);
+}
+
+extern "C" int gi_route_combine(const float* part, const float* weights, const int* pair_row, float* y, int T, int D, int top, void* stream) {
+    return gi::dispatch(gi_route_combine_impl, part, weights, pair_row, y, T, D, top, stream);
 }

@@ -356,31 +356,69 @@ def grouped_tile_rows() -> int:
     return int(lib().gi_grouped_tile_rows())
 
 
-def route_tiles(n_tokens: int, top: int, experts: int) -> int:
+TC_TILE_ROWS = 128       # token rows per tile of the tensor-core product that takes a matrix per tile
+
+
+def route_tiles(n_tokens: int, top: int, experts: int, tile_rows: Optional[int] = None) -> int:
     """An upper bound of the tiles that the (token, choice) pairs of a step make once bucketed by expert."""
     pairs = n_tokens * top
-    tm = grouped_tile_rows()
+    tm = tile_rows or grouped_tile_rows()
     return (pairs + tm - 1) // tm + min(experts, pairs)
 
 
 def route(x: torch.Tensor, w: torch.Tensor, correction: Optional[torch.Tensor], top: int, ids: torch.Tensor,
-          weights: torch.Tensor, sorted_rows: torch.Tensor, tile_group: torch.Tensor, n_tiles: torch.Tensor) -> None:
+          weights: torch.Tensor, sorted_rows: torch.Tensor, tile_group: torch.Tensor, n_tiles: torch.Tensor,
+          tile_rows: Optional[int] = None, pair_row: Optional[torch.Tensor] = None) -> None:
     """Per row of ``x`` [T, D]: s = sigmoid(w x) with ``w`` [E, D] 32-bit; the ``top`` experts with the largest
     s + correction go to ``ids`` [T, top] and their s to ``weights`` [T, top]. The pairs (token, choice) are then
-    bucketed by expert into tiles of grouped_tile_rows() rows: ``sorted_rows`` (pair index or -1), ``tile_group``
-    (a tile's expert), ``n_tiles`` [1]. Two launches."""
+    bucketed by expert into tiles of ``tile_rows`` rows (grouped_tile_rows() by default): ``sorted_rows`` (pair index
+    or -1), ``tile_group`` (a tile's expert), ``n_tiles`` [1], and optionally ``pair_row`` [T * top], the row each pair
+    landed in. Two launches."""
     T, D = x.shape
     E = w.shape[0]
     max_tiles = tile_group.numel()
+    tm = tile_rows or grouped_tile_rows()
     if w.shape != (E, D) or ids.shape != (T, top) or weights.shape != (T, top) or (correction is not None and correction.numel() != E):
         raise KernelError("route: shapes do not agree")
-    if sorted_rows.numel() < max_tiles * grouped_tile_rows() or max_tiles < route_tiles(T, top, E):
+    if sorted_rows.numel() < max_tiles * tm or max_tiles < route_tiles(T, top, E, tm) or (pair_row is not None and pair_row.numel() < T * top):
         raise KernelError("route: the buffers of the tiles are too small")
     check(lib().gi_route(_dev(x, "x"), dtype_code(x.dtype), T, D, _dev(w, "w", torch.float32), _opt(correction, "correction", torch.float32),
                          E, int(top), _dev(ids, "ids", torch.int32), _dev(weights, "weights", torch.float32),
                          _dev(sorted_rows, "sorted_rows", torch.int32), _dev(tile_group, "tile_group", torch.int32),
-                         _dev(n_tiles, "n_tiles", torch.int32), max_tiles, _stream()), "route")
+                         _dev(n_tiles, "n_tiles", torch.int32), max_tiles, tm, _opt(pair_row, "pair_row", torch.int32), _stream()), "route")
     count_launches(1)
+
+
+def gather_rows(x: torch.Tensor, a_div: int, sorted_rows: torch.Tensor, n_tiles: torch.Tensor, tile_rows: int, out: torch.Tensor) -> None:
+    """out[r] = x[sorted_rows[r] // a_div] for the rows of the first n_tiles tiles (zeros where sorted_rows is -1)."""
+    if out.shape[1] != x.shape[1] or out.dtype != x.dtype or sorted_rows.numel() < out.shape[0]:
+        raise KernelError("gather_rows: shapes do not agree")
+    check(lib().gi_gather_rows(_dev(x, "x"), dtype_code(x.dtype), x.shape[1], int(a_div), _dev(sorted_rows, "sorted_rows", torch.int32),
+                               _dev(n_tiles, "n_tiles", torch.int32), int(tile_rows), out.shape[0], _dev(out, "out"), _stream()), "gather_rows")
+
+
+def expert_product_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, tile_group: torch.Tensor, n_tiles: torch.Tensor,
+                      gated: Optional[str] = None) -> None:
+    """The same on the tensor cores (bfloat16) for rows already in the tiles' order: ``a`` [tiles * 128, K], tile i
+    multiplies ``w[tile_group[i]]``; ``out`` [tiles * 128, N] 32-bit, or gated: bfloat16 act(gate) * up."""
+    E, rows, K = w.shape
+    N = rows // 2 if gated else rows
+    M = a.shape[0]
+    if a.shape != (M, K) or out.shape != (M, N) or M % TC_TILE_ROWS or tile_group.numel() < M // TC_TILE_ROWS:
+        raise KernelError("expert_product_tc: shapes do not agree")
+    if gated is not None and gated not in ACTIVATIONS:
+        raise KernelError(f"expert_product_tc: unknown activation '{gated}'")
+    st = _tc_state(a.device)
+    check(lib().gi_gemm_tc_grouped(_dev(a, "a", torch.bfloat16), _dev(w, "w", torch.bfloat16),
+                                   _dev(out, "out", torch.bfloat16 if gated else torch.float32),
+                                   (2 | (ACTIVATIONS[gated] << 8)) if gated else 0, M, N, K, E,
+                                   _dev(tile_group, "tile_group", torch.int32), _dev(n_tiles, "n_tiles", torch.int32),
+                                   st.status.data_ptr(), _stream()), "expert_product_tc")
+
+
+def expert_product_tc_supported(N: int, K: int, gated: bool) -> bool:
+    """Rows that TMA can address: K a multiple of 8, output rows of a multiple of 16 bytes."""
+    return K % 8 == 0 and (N % 8 == 0 if gated else N % 4 == 0)
 
 
 def expert_product(a: torch.Tensor, a_div: int, w: torch.Tensor, out: torch.Tensor, sorted_rows: torch.Tensor,
@@ -400,14 +438,16 @@ def expert_product(a: torch.Tensor, a_div: int, w: torch.Tensor, out: torch.Tens
                                   tile_group.numel(), _stream()), "expert_product")
 
 
-def route_combine(part: torch.Tensor, weights: torch.Tensor, y: torch.Tensor) -> None:
-    """y[t] += sum_k weights[t, k] * part[t * top + k], in the order of k; all 32-bit."""
+def route_combine(part: torch.Tensor, weights: torch.Tensor, y: torch.Tensor, pair_row: Optional[torch.Tensor] = None) -> None:
+    """y[t] += sum_k weights[t, k] * part[row of pair t * top + k], in the order of k; all 32-bit. The row of a pair is
+    the pair itself, or ``pair_row[pair]`` when given."""
     T, D = y.shape
     top = weights.shape[1]
-    if part.shape != (T * top, D) or weights.shape[0] != T:
+    if part.dim() != 2 or part.shape[1] != D or weights.shape[0] != T or (pair_row is None and part.shape[0] != T * top) or \
+            (pair_row is not None and pair_row.numel() < T * top):
         raise KernelError("route_combine: shapes do not agree")
     check(lib().gi_route_combine(_dev(part, "part", torch.float32), _dev(weights, "weights", torch.float32),
-                                 _dev(y, "y", torch.float32), T, D, top, _stream()), "route_combine")
+                                 _opt(pair_row, "pair_row", torch.int32), _dev(y, "y", torch.float32), T, D, top, _stream()), "route_combine")
 
 
 def causal_conv(proj: torch.Tensor, offset: int, weight: torch.Tensor, bias: torch.Tensor, state: torch.Tensor,

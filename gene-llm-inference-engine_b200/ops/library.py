@@ -46,8 +46,10 @@ _SIGNATURES = {
     "gi_expert_product": [c_void_p, c_int, c_longlong, c_int, c_void_p, c_int, c_longlong, c_int, c_longlong, c_int, c_int,
                           c_void_p, c_int, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
     "gi_route": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
-                 c_void_p, c_int, c_void_p],
-    "gi_route_combine": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+                 c_void_p, c_int, c_int, c_void_p, c_void_p],
+    "gi_gather_rows": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p],
+    "gi_route_combine": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    "gi_gemm_tc_grouped": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
     "gi_grouped_tile_rows": [],
     "gi_causal_conv": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_longlong, c_longlong, c_void_p, c_void_p,
                        c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],

@@ -69,9 +69,14 @@ class RoutedExpertsFeedForward:
     ("silu"). Weights: ``router`` [E, hidden], ``correction`` [E], ``w_gate_up`` [E, 2I, hidden] (an expert's gate rows,
     then its up rows), ``w_down`` [E, hidden, I].
 
-    The step's (token, choice) pairs are bucketed by expert on the device into tiles of a few rows; each tile runs
-    its expert's matrices. The launches depend on the token count only (tiles beyond the step's number leave at once),
-    so the part is recorded into launch programs and CUDA graphs like the dense one."""
+    The step's (token, choice) pairs are bucketed by expert on the device into tiles of rows; each tile runs its
+    expert's matrices. Few pairs (decoding) and the 32-bit path: tiles of a few rows on the CUDA cores, the expert
+    weights streamed once. Many pairs in bfloat16: the rows are gathered into tiles of 128 in the experts' order and
+    the two products run on the tensor cores (the many-token product with a matrix per token tile, the activation in
+    the first one's epilogue). The launches depend on the token count only (tiles beyond the step's number are not
+    run), so the part is recorded into launch programs and CUDA graphs like the dense one."""
+
+    TC_FROM_PAIRS = 256        # from this many (token, choice) pairs on the tensor-core form runs
 
     graph_safe = True
 
@@ -101,6 +106,10 @@ class RoutedExpertsFeedForward:
         T = xn.shape[0]
         E, I, D, top = self.experts, self.intermediate_size, self.hidden_size, self.top
         most = getattr(ctx, "max_step_tokens", T)
+        if self.dtype is torch.bfloat16 and T * top >= self.TC_FROM_PAIRS and \
+                kernels.expert_product_tc_supported(I, D, True) and kernels.expert_product_tc_supported(D, I, False):
+            self._forward_tensor_cores(ctx, xn, x, max(most, T))
+            return
         tm = kernels.grouped_tile_rows()
         tiles, most_tiles = kernels.route_tiles(T, top, E), kernels.route_tiles(max(most, T), top, E)
         ids = ctx.scratch("route_ids", (T, top), torch.int32)
@@ -114,3 +123,24 @@ class RoutedExpertsFeedForward:
         part = ctx.scratch("expert_out", (T * top, D), torch.float32, capacity=max(most, T) * top)
         kernels.expert_product(hidden, 1, self.w_down, part, sorted_rows, tile_group, n_tiles)
         kernels.route_combine(part, weights, x)
+
+    def _forward_tensor_cores(self, ctx, xn: torch.Tensor, x: torch.Tensor, most: int) -> None:
+        T = xn.shape[0]
+        E, I, D, top = self.experts, self.intermediate_size, self.hidden_size, self.top
+        tm = kernels.TC_TILE_ROWS
+        tiles, most_tiles = kernels.route_tiles(T, top, E, tm), kernels.route_tiles(most, top, E, tm)
+        ids = ctx.scratch("route_ids", (T, top), torch.int32)
+        weights = ctx.scratch("route_weights", (T, top), torch.float32)
+        sorted_rows = ctx.scratch("route_sorted_rows_tc", (tiles * tm,), torch.int32, capacity=most_tiles * tm)
+        tile_group = ctx.scratch("route_tile_group_tc", (tiles,), torch.int32, capacity=most_tiles)
+        pair_row = ctx.scratch("route_pair_row", (T * top,), torch.int32, capacity=most * top)
+        n_tiles = ctx.scratch("route_n_tiles", (1,), torch.int32, capacity=1)
+        kernels.route(xn, self.router, self.correction, top, ids, weights, sorted_rows, tile_group, n_tiles, tile_rows=tm,
+                      pair_row=pair_row)
+        rows = ctx.scratch("expert_rows", (tiles * tm, D), self.dtype, capacity=most_tiles * tm)
+        kernels.gather_rows(xn, top, sorted_rows, n_tiles, tm, rows)
+        hidden = ctx.scratch("expert_hidden_tc", (tiles * tm, I), self.dtype, capacity=most_tiles * tm)
+        kernels.expert_product_tc(rows, self.w_gate_up, hidden, tile_group, n_tiles, gated=self.activation)
+        part = ctx.scratch("expert_out_tc", (tiles * tm, D), torch.float32, capacity=most_tiles * tm)
+        kernels.expert_product_tc(hidden, self.w_down, part, tile_group, n_tiles)
+        kernels.route_combine(part, weights, x, pair_row=pair_row)

@@ -14,6 +14,16 @@ import torch
 F = torch.float64
 
 
+def ident(x: torch.Tensor) -> torch.Tensor:
+    return x
+
+
+def bf16(x: torch.Tensor) -> torch.Tensor:
+    """Rounds to bfloat16 and back: what an engine that keeps the operands of its matrix products and its cache in
+    bfloat16 does to them (the functions below take it as ``rnd`` and apply it at those places)."""
+    return x.to(torch.bfloat16).to(F)
+
+
 # ---------------------------------------------------------------------------------------------- small pieces
 def unit_rms(x: torch.Tensor, eps: float) -> torch.Tensor:
     """x / sqrt(mean(x^2) + eps) over the last dimension."""
@@ -94,14 +104,15 @@ def softmax_rows(scores: torch.Tensor, mask: torch.Tensor, sink: Optional[torch.
 
 
 # ---------------------------------------------------------------------------------------------- mixers
-def attention_mixer(h: torch.Tensor, m: dict, w: Dict[str, torch.Tensor], eps: float, positions: torch.Tensor) -> torch.Tensor:
+def attention_mixer(h: torch.Tensor, m: dict, w: Dict[str, torch.Tensor], eps: float, positions: torch.Tensor, rnd=ident) -> torch.Tensor:
     """Grouped-query attention without rotation: queries and keys brought to unit RMS per head, a bias that grows
     with the distance, blocks of positions that do not see each other, a sink per head."""
     n = h.shape[0]
     H, G, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
-    q = unit_rms((h @ w["q"].T).view(n, H, d), eps)
-    k = unit_rms((h @ w["k"].T).view(n, G, d), eps)
-    v = (h @ w["v"].T).view(n, G, dv)
+    h = rnd(h)
+    q = rnd(unit_rms((h @ w["q"].T).view(n, H, d), eps))
+    k = rnd(unit_rms((h @ w["k"].T).view(n, G, d), eps))
+    v = rnd((h @ w["v"].T).view(n, G, dv))
     per = H // G
     k = k.repeat_interleave(per, dim=1)
     v = v.repeat_interleave(per, dim=1)
@@ -110,33 +121,36 @@ def attention_mixer(h: torch.Tensor, m: dict, w: Dict[str, torch.Tensor], eps: f
     scores = scores - slope.view(H, 1, 1) * (positions[:, None] - positions[None, :]).to(F)[None]
     p = softmax_rows(scores, chunk_mask(positions, m["mask"]["size"]), w["sink"])
     out = torch.einsum("hij,jhd->ihd", p, v).reshape(n, H * dv)
-    return out @ w["o"].T
+    return rnd(out) @ w["o"].T
 
 
 def latent_attention_mixer(h: torch.Tensor, m: dict, w: Dict[str, torch.Tensor], eps: float, positions: torch.Tensor,
-                           sink: bool) -> torch.Tensor:
+                           second: bool, rnd=ident) -> torch.Tensor:
     """Attention whose queries, keys and values are made from low-rank latents; one rotated key part is shared by
-    the heads; a sliding window; with ``sink`` one more term in the denominator."""
+    the heads; a sliding window; the second kind scales the rotation for long contexts and has one more term in the
+    softmax's denominator."""
     n = h.shape[0]
     H, d, r, dv, rank = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
-    freq, amp = rotation_frequencies(m["rot"]["dims"], m["rot"]["base"], m["rot"].get("scaling"))
-    cq = rms_norm(h @ w["dq"].T, w["dq.norm"], eps)
+    freq, amp = rotation_frequencies(m["rot"]["dims"], m["rot"]["base"], m["rot"]["scaling"] if second else None)
+    h = rnd(h)
+    cq = rnd(rms_norm(h @ w["dq"].T, w["dq.norm"], eps))
     q = (cq @ w["uq"].T).view(n, H, d + r)
     q_plain, q_rot = q[..., :d], rotate_pairs(q[..., d:], positions, freq, amp)
     ckv = h @ w["dkv"].T
-    c = rms_norm(ckv[:, :rank], w["dkv.norm"], eps)
-    k_rot = rotate_pairs(ckv[:, rank:], positions, freq, amp)                    # [n, r], one for all heads
+    c = rnd(rms_norm(ckv[:, :rank], w["dkv.norm"], eps))
+    k_rot = rnd(rotate_pairs(ckv[:, rank:], positions, freq, amp))               # [n, r], one for all heads
     k_plain = (c @ w["uk"].T).view(n, H, d)
     v = (c @ w["uv"].T).view(n, H, dv)
     scores = (torch.einsum("ihd,jhd->hij", q_plain, k_plain) + torch.einsum("ihr,jr->hij", q_rot, k_rot)) * m["scale"]
-    p = softmax_rows(scores, window_mask(positions, m["mask"]["size"]), w["sink"] if sink else None)
+    p = softmax_rows(scores, window_mask(positions, m["mask"]["size"]), w["sink"] if second else None)
     out = torch.einsum("hij,jhd->ihd", p, v).reshape(n, H * dv)
-    return out @ w["o"].T
+    return rnd(out) @ w["o"].T
 
 
 # ---------------------------------------------------------------------------------------------- feed-forwards
-def dense_ff(h: torch.Tensor, w: Dict[str, torch.Tensor]) -> torch.Tensor:
-    return (gelu_tanh(h @ w["gate"].T) * (h @ w["up"].T)) @ w["down"].T
+def dense_ff(h: torch.Tensor, w: Dict[str, torch.Tensor], rnd=ident) -> torch.Tensor:
+    h = rnd(h)
+    return rnd(gelu_tanh(h @ w["gate"].T) * (h @ w["up"].T)) @ w["down"].T
 
 
 def route(h: torch.Tensor, router: torch.Tensor, correction: torch.Tensor, top: int) -> Tuple[torch.Tensor, torch.Tensor]:
@@ -147,7 +161,8 @@ def route(h: torch.Tensor, router: torch.Tensor, correction: torch.Tensor, top: 
     return chosen, torch.gather(s, 1, chosen)
 
 
-def moe_ff(h: torch.Tensor, mlp: dict, w: Dict[str, torch.Tensor]) -> torch.Tensor:
+def moe_ff(h: torch.Tensor, mlp: dict, w: Dict[str, torch.Tensor], rnd=ident) -> torch.Tensor:
+    h = rnd(h)
     chosen, weight = route(h, w["router"], w["correction"], mlp["router"]["top"])
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
@@ -163,7 +178,7 @@ def _sub(weights: Dict[str, torch.Tensor], prefix: str) -> Dict[str, torch.Tenso
     return {k[len(prefix):]: v.to(F) for k, v in weights.items() if k.startswith(prefix)}
 
 
-def forward(config: dict, weights: Dict[str, torch.Tensor], tokens: List[int]) -> Tuple[torch.Tensor, torch.Tensor]:
+def forward(config: dict, weights: Dict[str, torch.Tensor], tokens: List[int], rnd=ident) -> Tuple[torch.Tensor, torch.Tensor]:
     """(logits [n, vocab], the residual stream after every layer run [runs, n, width])."""
     eps = config["norm"]["eps"]
     positions = torch.arange(len(tokens))
@@ -175,17 +190,43 @@ def forward(config: dict, weights: Dict[str, torch.Tensor], tokens: List[int]) -
         mix = _sub(w, "mix.")
         kind, m = layer["type"], layer["mixer"]
         if kind == "attention":
-            y = attention_mixer(x, m, mix, eps, positions)
+            y = attention_mixer(x, m, mix, eps, positions, rnd)
         elif kind in ("latent_attention", "latent_attention_2"):
-            y = latent_attention_mixer(x, m, mix, eps, positions, sink=kind == "latent_attention_2")
+            y = latent_attention_mixer(x, m, mix, eps, positions, kind == "latent_attention_2", rnd)
         else:
             raise ValueError(kind)
         x = x + rms_norm(y, w["norm1"], eps)
         mlp = layer.get("mlp")
         if mlp is not None:
             ff = _sub(w, "mlp.")
-            y = dense_ff(x, ff) if mlp["kind"] == "dense" else moe_ff(x, mlp, ff)
+            y = dense_ff(x, ff, rnd) if mlp["kind"] == "dense" else moe_ff(x, mlp, ff, rnd)
             x = x + rms_norm(y, w["norm2"], eps)
         after.append(x)
-    logits = rms_norm(x, weights["final.norm"].to(F), eps) @ weights["head"].to(F).T
+    logits = rnd(rms_norm(x, weights["final.norm"].to(F), eps)) @ weights["head"].to(F).T
     return logits, torch.stack(after)
+
+
+def load(folder: str) -> Tuple[dict, Dict[str, torch.Tensor]]:
+    """(config.json as a dictionary, the tensors of model.safetensors by name), read with a reader of its own."""
+    import json
+    import os
+    import struct
+    import numpy as np
+    with open(os.path.join(folder, "config.json")) as f:
+        config = json.load(f)
+    with open(os.path.join(folder, "model.safetensors"), "rb") as f:
+        n = struct.unpack("<Q", f.read(8))[0]
+        header = json.loads(f.read(n))
+        data = f.read()
+    out = {}
+    for name, e in header.items():
+        if name == "__metadata__":
+            continue
+        a, b = e["data_offsets"]
+        if e["dtype"] == "BF16":
+            bits = np.frombuffer(data[a:b], dtype="<u2").astype(np.uint32) << 16
+            t = torch.from_numpy(bits.view(np.float32).copy())
+        else:
+            t = torch.from_numpy(np.frombuffer(data[a:b], dtype="<f4").copy())
+        out[name] = t.view(e["shape"])
+    return config, out
