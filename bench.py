@@ -587,13 +587,13 @@ def run_nipadra(args):
 # ---------------------------------------------------------------------------------------------- Gekupel beside Llama
 def gekupel_config(width, ff, layers, vocab, heads, head_dim, kv_heads, span):
     """A Gekupel model with the layer sizes of a Llama shape: the attention layers have Llama's heads, the latent ones
-    half as many heads with a rotated part of half a head and latents of 3/8 (queries) and 1/4 (keys, values) of the
-    width; the mixture has 8 experts of half the dense width of which a token uses 2 (the dense layer's
+    half as many heads with a rotated part of half a head and latents of 3/8 (queries) and 1/4 (keys, values; at most
+    512) of the width; the mixture has 8 experts of half the dense width of which a token uses 2 (the dense layer's
     multiply-adds). Layers in turn: latent (scaled rotation, sink) with a dense feed-forward, attention with experts,
     latent with experts, attention with experts."""
     lh = max(heads // 2, 1)
     rot = {"base": 500000.0, "dims": head_dim // 2}
-    lat = {"dim": head_dim, "heads": lh, "kv_rank": width // 4, "mask": {"size": span}, "q_rank": 3 * width // 8, "rot": rot,
+    lat = {"dim": head_dim, "heads": lh, "kv_rank": min(512, width // 4), "mask": {"size": span}, "q_rank": 3 * width // 8, "rot": rot,
            "rot_dim": head_dim // 2, "scale": (head_dim + head_dim // 2) ** -0.5, "vdim": head_dim}
     lat2 = dict(lat, rot=dict(rot, scaling={"factor": 4.0, "fast": 32.0, "original": 8192, "slow": 1.0}))
     att = {"dim": head_dim, "heads": heads, "kv_heads": kv_heads, "mask": {"size": span}, "scale": head_dim ** -0.5, "vdim": head_dim}
@@ -630,7 +630,7 @@ def gekupel_kernel_table(width, heads, kv_heads, head_dim, span, ff, T, pk):
         rows.append(row)
 
     D, page = width, 16
-    lh, rot, kr, qr = max(heads // 2, 1), head_dim // 2, width // 4, 3 * width // 8
+    lh, rot, kr, qr = max(heads // 2, 1), head_dim // 2, min(512, width // 4), 3 * width // 8
     E, top, I = 8, 2, ff // 2
     for what, R, n in (("prefill", 1, T), ("decode", 8, 1)):
         N = R * n
@@ -662,9 +662,24 @@ def gekupel_kernel_table(width, heads, kv_heads, head_dim, span, ff, T, pk):
         ol = torch.empty(N, lh * kr, device=dev)
         seen = sum(min(span, p + 1) for p in range(T - n, T))
         lat_bytes = R * min(T, span + n) * (kr + rot) * 2 + N * lh * (2 * kr + rot) * 4
+        def listed(Hq, Hk, hd_, vd_, alias):
+            """The rows as the mixers hand them over: tiles of a prompt portion, or single tokens; few tiles in ranges of keys."""
+            pt = K.attention_rows_tile_tokens(Hq, Hk, hd_, vd_, alias)
+            if n == 1:
+                kw = {"rows": torch.arange(R, **i32)}
+                count = R
+            else:
+                kw = {"tiles": torch.tensor([(t, min(pt, n - t), 0) for t in range(0, n, pt)][::-1], **i32)}
+                count = kw["tiles"].shape[0]
+            sp = K.attention_rows_splits(count, Hq, Hk, span)
+            if sp > 1:
+                kw.update(splits=sp, workspace=torch.empty(K.attention_rows_workspace_rows(count, Hq, Hk, sp), vd_ + 2, device=dev))
+            return kw
+
+        lat_kw = listed(lh, 1, kr + rot, kr, True)
         add(f"attention_rows over the latent, window {span} ({what})", "attention",
-            lambda: K.attention_rows(qa, cache, None, ol, rr, pos, tables, lh, 1, kr + rot, kr, page, 0.1, window=span),
-            lat_bytes, flops=2.0 * R * seen * lh * (2 * kr + rot), simt=R * seen * lh * (2 * kr + rot))
+            lambda: K.attention_rows(qa, cache, None, ol, rr, pos, tables, lh, 1, kr + rot, kr, page, 0.1, window=span, **lat_kw),
+            lat_bytes, flops=2.0 * R * seen * lh * (2 * kr + rot))
         wuv = (torch.randn(lh, head_dim, kr, device=dev) * 0.05).to(bf)
         att = torch.empty(N, lh * head_dim, dtype=bf, device=dev)
         add(f"head_product, values ({what})", "product", lambda: K.head_product(ol, 0, kr, wuv, att, 0, head_dim),
@@ -676,11 +691,11 @@ def gekupel_kernel_table(width, heads, kv_heads, head_dim, span, ff, T, pk):
         o2 = torch.empty_like(q2)
         slopes, sinks = torch.rand(heads, device=dev) * 0.1, torch.randn(heads, device=dev)
         seen_c = sum(p % span + 1 for p in range(T - n, T))
+        att_kw = listed(heads, kv_heads, head_dim, head_dim, False)
         add(f"attention_rows in blocks of {span} with bias and sinks ({what})", "attention",
             lambda: K.attention_rows(q2, kc, vc, o2, rr, pos, tables, heads, kv_heads, head_dim, head_dim, page, head_dim ** -0.5,
-                                     chunk=span, slopes=slopes, sinks=sinks),
-            R * min(T, span) * kv_heads * head_dim * 4 + N * heads * head_dim * 4, flops=4.0 * R * seen_c * heads * head_dim,
-            simt=2.0 * R * seen_c * heads * head_dim)
+                                     chunk=span, slopes=slopes, sinks=sinks, **att_kw),
+            R * min(T, span) * kv_heads * head_dim * 4 + N * heads * head_dim * 4, flops=4.0 * R * seen_c * heads * head_dim)
         rows_dec = torch.arange(R, **i32)
         per_tile = 128 // (heads // kv_heads)
         work = torch.tensor([(t, min(per_tile, n - t), 0) for t in range(0, n, per_tile)][::-1], **i32)

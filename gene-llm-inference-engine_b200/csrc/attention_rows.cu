@@ -183,6 +183,337 @@ attention_rows_kernel(const RowsArgs a) {
     }
 }
 
+// ------------------------------------------------------------------------------------------------ tensor cores
+// The same attention for a bfloat16 cache on the tensor cores (mma.sync m16n8k16): one block per (tile of query rows,
+// key/value head, block of query heads, range of the keys). The sixteen rows of an MMA tile are the query heads of a
+// group: all sixteen of one token where a key/value head serves sixteen or more heads (attention over a shared latent:
+// all heads read one row per key), or the heads of several consecutive tokens of one request where it serves fewer
+// (16 / group tokens; every row has its own position and so its own first and last visible key). Key tiles of 32 rows
+// come through cp.async into two stages; the four warps share a tile's work: each takes every fourth 16-wide slice of
+// the head dimension of S = Q K^T (the partial sums meet in shared memory and are added in warp order) and a quarter of
+// the value dimensions of O += P V, so the accumulators of a 512-wide value are 64 registers a thread. Scores,
+// softmax, bias and sinks are 32-bit as above; queries and the softmax's weights are rounded to bfloat16 where they
+// enter a product. With few tiles (decoding) the keys are cut into ``splits`` ranges that run side by side and leave
+// unnormalised sums, maxima and weights in a workspace, which a second kernel merges in the ranges' order.
+__device__ __forceinline__ void rows_cp_async16(uint32_t dst, const void* src, int bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void rows_cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void rows_cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void rows_ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void rows_ldsm_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void rows_mma(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t rows_pack(float lo, float hi) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&v);
+}
+__device__ __forceinline__ uint32_t rows_smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+constexpr int kMmaHeads = 16;          // rows of an MMA tile
+constexpr int kMmaPad = 8;             // bfloat16 values of padding per row of a tile (16 bytes: ldmatrix without conflicts)
+constexpr int kMmaSStride = kRowsTile + 4;
+
+// Which rows of the step a block works on: tile b of the list.
+struct RowTiles {
+    const int* list;       // kind 1: the row of tile b; kind 2: (first row, tokens, request) of tile b; kind 0: tile b = row b
+    int kind;
+    int head_blocks;       // blocks of sixteen heads per key/value head (groups of more than sixteen heads)
+    int splits;            // ranges of keys that run side by side (> 1: results go through ``workspace``)
+    float* workspace;      // [tiles][Hkv][head_blocks][splits][16][vd + 2]
+};
+
+struct TileRows {
+    int row0, ntok, gp;
+    __device__ __forceinline__ int token(int r) const { return gp == kMmaHeads ? 0 : r / gp; }
+    __device__ __forceinline__ int head(int r) const { return gp == kMmaHeads ? r : r % gp; }
+};
+__device__ __forceinline__ TileRows tile_rows(const RowTiles& rt, int b, int group) {
+    TileRows t;
+    if (rt.kind == 2) { t.row0 = rt.list[3 * b]; t.ntok = rt.list[3 * b + 1]; }
+    else { t.row0 = rt.kind == 1 ? rt.list[b] : b; t.ntok = 1; }
+    t.gp = min(group, kMmaHeads);
+    return t;
+}
+__device__ __forceinline__ int first_visible(const RowsArgs& a, int pos) {
+    int lo = 0;
+    if (a.window > 0) lo = max(lo, pos - a.window + 1);
+    if (a.chunk > 0) lo = max(lo, pos / a.chunk * a.chunk);
+    return lo;
+}
+
+// NV: 8-wide tiles of value dimensions per warp (vd <= 32 NV).
+template <int NV>
+__global__ void __launch_bounds__(128)
+attention_rows_mma_kernel(const RowsArgs a, const RowTiles rt) {
+    pdl_prologue();
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    using bf = __nv_bfloat16;
+    const int g = blockIdx.y;
+    const int group = a.H / a.Hkv;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int zb = blockIdx.z % rt.head_blocks, split = blockIdx.z / rt.head_blocks;
+    const TileRows tr = tile_rows(rt, blockIdx.x, group);
+    const int first_head = zb * kMmaHeads;
+    const int n_heads = min(kMmaHeads, group - first_head);
+    const int n_rows = tr.gp == kMmaHeads ? n_heads : tr.ntok * tr.gp;
+    const int qs = a.hd + kMmaPad;                     // row length of the query and key tiles
+    const int vs = a.alias ? qs : a.vd + kMmaPad;
+    bf* s_q = reinterpret_cast<bf*>(smem_raw);                              // [16][qs]
+    bf* s_k = s_q + kMmaHeads * qs;                                         // [2][32][qs]
+    bf* s_v = a.alias ? s_k : s_k + 2 * kRowsTile * qs;                     // [2][32][vs]
+    float* s_s = reinterpret_cast<float*>(s_k + 2 * kRowsTile * qs + (a.alias ? 0 : 2 * kRowsTile * vs));   // [4][16][36]
+
+    const int pos0 = a.positions[tr.row0];
+    const int lo_t = first_visible(a, pos0), hi_t = pos0 + tr.ntok - 1;     // the keys that some row of the tile sees
+    const int* table = a.block_tables + static_cast<size_t>(a.row_req[tr.row0]) * a.table_stride;
+    const bf* kc = static_cast<const bf*>(a.k_cache);
+    const bf* vc = static_cast<const bf*>(a.v_cache);
+    const int k_chunks = a.hd / 8, v_chunks = a.vd / 8;
+    const int all_tiles = (hi_t - lo_t) / kRowsTile + 1;
+    const int per_split = (all_tiles + rt.splits - 1) / rt.splits;
+    const int it0 = split * per_split, it1 = min(all_tiles, it0 + per_split);
+
+    auto fetch = [&](int tile, int stage) {
+        const int base = lo_t + tile * kRowsTile;
+        for (int j = warp; j < kRowsTile; j += 4) {
+            const int p = base + j;
+            const bool in = p <= hi_t;
+            size_t row = 0;
+            if (in) row = (static_cast<size_t>(table[p / a.page_size]) * a.Hkv + g) * a.page_size + (p % a.page_size);
+            const bf* src = kc + row * a.hd;
+            const uint32_t dst = rows_smem_u32(s_k + (stage * kRowsTile + j) * qs);
+            for (int c = lane; c < k_chunks; c += 32) rows_cp_async16(dst + c * 16, src + c * 8, in ? 16 : 0);   // 0 bytes: zeros
+            if (!a.alias) {
+                const bf* vsrc = vc + row * a.v_row;
+                const uint32_t vdst = rows_smem_u32(s_v + (stage * kRowsTile + j) * vs);
+                for (int c = lane; c < v_chunks; c += 32) rows_cp_async16(vdst + c * 16, vsrc + c * 8, in ? 16 : 0);
+            }
+        }
+        rows_cp_async_commit();
+    };
+
+    if (it0 < it1) fetch(it0, 0);
+    for (int i = threadIdx.x; i < kMmaHeads * a.hd; i += 128) {
+        const int r = i / a.hd, d = i % a.hd;
+        float v = 0.f;
+        if (r < n_rows) {
+            const size_t off = static_cast<size_t>(tr.row0 + tr.token(r)) * a.ldq +
+                               static_cast<size_t>(g * group + first_head + tr.head(r)) * a.hd + d;
+            v = a.q_is_f32 ? static_cast<const float*>(a.q)[off] : to_float(static_cast<const bf*>(a.q)[off]);
+        }
+        s_q[r * qs + d] = __float2bfloat16_rn(v);
+    }
+
+    const int gr = lane >> 2, tq = lane & 3;            // the fragment's rows gr and gr + 8 and its pair of columns
+    float o[NV][4];
+#pragma unroll
+    for (int i = 0; i < NV; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f}, slope[2] = {0.f, 0.f};
+    int pos_r[2], lo_r[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const int r = gr + 8 * h;
+        const bool row_on = r < n_rows;
+        pos_r[h] = row_on ? pos0 + tr.token(r) : -1;              // a row that is not there sees no key
+        lo_r[h] = row_on ? first_visible(a, pos_r[h]) : 0;
+        if (a.slopes && row_on) slope[h] = a.slopes[g * group + first_head + tr.head(r)];
+    }
+    const int nv = a.vd / 32;                            // 8-wide value tiles of this warp
+    const int v0 = warp * (a.vd / 4);                    // its first value dimension
+    const int k_steps = a.hd / 16;
+
+    for (int it = it0; it < it1; ++it) {
+        const int st = (it - it0) & 1;
+        rows_cp_async_wait_all();
+        __syncthreads();                                 // tile ``it`` is there; everyone is done with the other stage
+        if (it + 1 < it1) fetch(it + 1, st ^ 1);
+        const bf* kt = s_k + st * kRowsTile * qs;
+        const bf* vt = s_v + st * kRowsTile * vs;
+        // S = Q K^T, this warp's slices of the head dimension
+        float s[4][4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f; }
+        for (int ks = warp; ks < k_steps; ks += 4) {
+            uint32_t qa[4];
+            rows_ldsm_x4(rows_smem_u32(s_q + (lane & 15) * qs + ks * 16 + (lane >> 4) * 8), qa[0], qa[1], qa[2], qa[3]);
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                uint32_t b0, b1, b2, b3;
+                rows_ldsm_x4(rows_smem_u32(kt + (half * 16 + (lane >> 4) * 8 + (lane & 7)) * qs + ks * 16 + ((lane >> 3) & 1) * 8), b0, b1, b2, b3);
+                rows_mma(s[half * 2], qa, b0, b1);
+                rows_mma(s[half * 2 + 1], qa, b2, b3);
+            }
+        }
+        float* mine = s_s + warp * kMmaHeads * kMmaSStride;
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt) {
+            mine[gr * kMmaSStride + nt * 8 + 2 * tq] = s[nt][0];
+            mine[gr * kMmaSStride + nt * 8 + 2 * tq + 1] = s[nt][1];
+            mine[(gr + 8) * kMmaSStride + nt * 8 + 2 * tq] = s[nt][2];
+            mine[(gr + 8) * kMmaSStride + nt * 8 + 2 * tq + 1] = s[nt][3];
+        }
+        __syncthreads();
+        // every warp adds the four partial sums in warp order and takes the softmax step of all sixteen rows
+        const int base = lo_t + it * kRowsTile;
+        float tile_max[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int h = e >> 1, r = gr + h * 8, col = nt * 8 + 2 * tq + (e & 1);
+                float v = 0.f;
+#pragma unroll
+                for (int w = 0; w < 4; ++w) v += s_s[(w * kMmaHeads + r) * kMmaSStride + col];
+                const int key = base + col;
+                v = (key >= lo_r[h] && key <= pos_r[h]) ? v * a.scale - slope[h] * static_cast<float>(pos_r[h] - key) : -INFINITY;
+                s[nt][e] = v;
+                tile_max[h] = fmaxf(tile_max[h], v);
+            }
+        }
+        float corr[2], sum[2] = {0.f, 0.f};
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            tile_max[h] = fmaxf(tile_max[h], __shfl_xor_sync(0xffffffffu, tile_max[h], 1));
+            tile_max[h] = fmaxf(tile_max[h], __shfl_xor_sync(0xffffffffu, tile_max[h], 2));
+            const float m_new = fmaxf(m[h], tile_max[h]);            // -inf while the row has seen no key yet
+            corr[h] = m[h] == -INFINITY ? 0.f : expf(m[h] - m_new);
+            m[h] = m_new;
+        }
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float p = s[nt][e] == -INFINITY ? 0.f : expf(s[nt][e] - m[e >> 1]);
+                s[nt][e] = p;
+                sum[e >> 1] += p;
+            }
+        }
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            sum[h] += __shfl_xor_sync(0xffffffffu, sum[h], 1);
+            sum[h] += __shfl_xor_sync(0xffffffffu, sum[h], 2);
+            l[h] = l[h] * corr[h] + sum[h];
+        }
+#pragma unroll
+        for (int i = 0; i < NV; ++i) { o[i][0] *= corr[0]; o[i][1] *= corr[0]; o[i][2] *= corr[1]; o[i][3] *= corr[1]; }
+        // O += P V, this warp's quarter of the value dimensions
+#pragma unroll
+        for (int ks = 0; ks < 2; ++ks) {
+            uint32_t pa[4] = {rows_pack(s[2 * ks][0], s[2 * ks][1]), rows_pack(s[2 * ks][2], s[2 * ks][3]),
+                              rows_pack(s[2 * ks + 1][0], s[2 * ks + 1][1]), rows_pack(s[2 * ks + 1][2], s[2 * ks + 1][3])};
+#pragma unroll
+            for (int np = 0; np < NV / 2; ++np) {
+                if (2 * np < nv) {
+                    uint32_t b0, b1, b2, b3;
+                    rows_ldsm_x4_trans(rows_smem_u32(vt + (ks * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * vs + v0 + np * 16 + (lane >> 4) * 8),
+                                       b0, b1, b2, b3);
+                    rows_mma(o[2 * np], pa, b0, b1);
+                    rows_mma(o[2 * np + 1], pa, b2, b3);
+                }
+            }
+        }
+    }
+    rows_cp_async_wait_all();
+
+    if (rt.splits > 1) {
+        // this range's unnormalised sums, maximum and weight: merged by attention_rows_merge_kernel
+        float* ws = rt.workspace + ((((static_cast<size_t>(blockIdx.x) * a.Hkv + g) * rt.head_blocks + zb) * rt.splits + split) * kMmaHeads) * (a.vd + 2);
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            float* row = ws + static_cast<size_t>(gr + 8 * h) * (a.vd + 2);
+#pragma unroll
+            for (int i = 0; i < NV; ++i) {
+                if (i < nv) { row[v0 + i * 8 + 2 * tq] = o[i][2 * h]; row[v0 + i * 8 + 2 * tq + 1] = o[i][2 * h + 1]; }
+            }
+            if (warp == 0 && tq == 0) { row[a.vd] = m[h]; row[a.vd + 1] = l[h]; }
+        }
+        return;
+    }
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const int r = gr + 8 * h;
+        if (r >= n_rows) continue;
+        const int head = g * group + first_head + tr.head(r);
+        float M = m[h], L = l[h], f = 1.f;
+        if (a.sinks) {
+            const float sk = a.sinks[head];
+            M = fmaxf(M, sk);
+            f = expf(m[h] - M);
+            L = L * f + expf(sk - M);
+        }
+        const float mul = f / L;
+        const size_t ob = static_cast<size_t>(tr.row0 + tr.token(r)) * a.ldo + static_cast<size_t>(head) * a.vd + v0 + 2 * tq;
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            if (i < nv) {
+                const float x0 = o[i][2 * h] * mul, x1 = o[i][2 * h + 1] * mul;
+                if (a.out_is_f32) *reinterpret_cast<float2*>(static_cast<float*>(a.out) + ob + i * 8) = make_float2(x0, x1);
+                else *reinterpret_cast<uint32_t*>(static_cast<bf*>(a.out) + ob + i * 8) = rows_pack(x0, x1);
+            }
+        }
+    }
+}
+
+// Merges the ranges of keys of a tile, in their order: one block per (tile, key/value head, block of heads), a warp per row.
+__global__ void __launch_bounds__(128)
+attention_rows_merge_kernel(const RowsArgs a, const RowTiles rt) {
+    pdl_prologue();
+    const int g = blockIdx.y, zb = blockIdx.z;
+    const int group = a.H / a.Hkv;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const TileRows tr = tile_rows(rt, blockIdx.x, group);
+    const int first_head = zb * kMmaHeads;
+    const int n_rows = tr.gp == kMmaHeads ? min(kMmaHeads, group - first_head) : tr.ntok * tr.gp;
+    const size_t stride = static_cast<size_t>(kMmaHeads) * (a.vd + 2);
+    const float* ws = rt.workspace + (((static_cast<size_t>(blockIdx.x) * a.Hkv + g) * rt.head_blocks + zb) * rt.splits) * stride;
+    for (int r = warp; r < n_rows; r += 4) {
+        const int head = g * group + first_head + tr.head(r);
+        const float* row = ws + static_cast<size_t>(r) * (a.vd + 2);
+        float M = a.sinks ? a.sinks[head] : -INFINITY;
+        for (int s = 0; s < rt.splits; ++s) M = fmaxf(M, row[s * stride + a.vd]);
+        float L = a.sinks ? expf(a.sinks[head] - M) : 0.f;
+        for (int s = 0; s < rt.splits; ++s) {
+            const float ms = row[s * stride + a.vd];
+            if (ms != -INFINITY) L += row[s * stride + a.vd + 1] * expf(ms - M);
+        }
+        const size_t ob = static_cast<size_t>(tr.row0 + tr.token(r)) * a.ldo + static_cast<size_t>(head) * a.vd;
+        for (int d = lane; d < a.vd; d += 32) {
+            float v = 0.f;
+            for (int s = 0; s < rt.splits; ++s) {
+                const float ms = row[s * stride + a.vd];
+                if (ms != -INFINITY) v += row[s * stride + d] * expf(ms - M);
+            }
+            v /= L;
+            if (a.out_is_f32) static_cast<float*>(a.out)[ob + d] = v;
+            else static_cast<__nv_bfloat16*>(a.out)[ob + d] = __float2bfloat16_rn(v);
+        }
+    }
+}
+
+template <int NV>
+static int launch_rows_mma(const RowsArgs& a, const RowTiles& rt, int n_tiles, size_t smem, cudaStream_t st) {
+    auto kernel = attention_rows_mma_kernel<NV>;
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+        if (e != cudaSuccess) { set_error("attention_rows: %s", cudaGetErrorString(e)); return 1; }
+    }
+    launch_kernel(kernel, dim3(n_tiles, a.Hkv, rt.head_blocks * rt.splits), dim3(128), smem, st, a, rt);
+    if (check_launch("attention_rows (tensor cores)")) return 1;
+    if (rt.splits > 1) {
+        launch_kernel(attention_rows_merge_kernel, dim3(n_tiles, a.Hkv, rt.head_blocks), dim3(128), 0, st, a, rt);
+        return check_launch("attention_rows (merge)");
+    }
+    return 0;
+}
+
 constexpr int kRowsMaxValueDim = 512;
 constexpr int kRowsMaxHeadDim = 1024;
 
@@ -208,16 +539,37 @@ static int launch_rows_vi(const RowsArgs& a, int T_rows, int blocks_z, int warps
 
 using namespace gi;
 
+static int g_rows_mma = 1;
+// 0: the CUDA-core form also where the tensor-core form applies (for comparisons); returns the old setting
+extern "C" int gi_attention_rows_set_mma(int on) { const int old = g_rows_mma; g_rows_mma = on ? 1 : 0; return old; }
+
 extern "C" int gi_attention_rows_supported(int hd, int vd) {
     return hd >= 1 && hd <= kRowsMaxHeadDim && vd >= 1 && vd <= kRowsMaxValueDim;
+}
+
+static size_t rows_mma_smem(int hd, int vd, bool alias) {
+    const int qs = hd + kMmaPad, vs = vd + kMmaPad;
+    return static_cast<size_t>(kMmaHeads + 2 * kRowsTile) * qs * 2 + (alias ? 0 : static_cast<size_t>(2 * kRowsTile) * vs * 2) +
+           static_cast<size_t>(4 * kMmaHeads * kMmaSStride) * 4;
+}
+
+// How many consecutive tokens of one request share a tile of the tensor-core form (16 / group, at least 1), or 0 when
+// that form does not serve these sizes (a bfloat16 cache is understood): the head size in whole 16s, the value size
+// in whole 64s up to 512.
+extern "C" int gi_attention_rows_tile_tokens(int H, int Hkv, int hd, int vd, int values_in_keys) {
+    if (!g_rows_mma || Hkv <= 0 || H % Hkv || hd % 16 || vd % 64 || vd > kRowsMaxValueDim || hd > kRowsMaxHeadDim) return 0;
+    if (rows_mma_smem(hd, vd, values_in_keys != 0) > 200 * 1024) return 0;
+    const int group = H / Hkv;
+    return group >= kMmaHeads ? 1 : kMmaHeads / group;
 }
 
 static int gi_attention_rows_impl(const void* q, int q_dtype, int ldq, const void* k_cache, const void* v_cache, int cache_dtype,
                                  void* out, int out_dtype, int ldo, const int* row_req, const int* positions,
                                  const int* block_tables, int table_stride, int T, int H, int Hkv, int hd, int vd, int v_row,
                                  int values_in_keys, int page_size, float scale, int window, int chunk, const float* slopes,
-                                 const float* sinks, void* stream) {
-    if (T == 0) return 0;
+                                 const float* sinks, const int* tile_list, int list_kind, int n_tiles, int splits, float* workspace,
+                                 long long workspace_floats, void* stream) {
+    if (T == 0 || (list_kind != 0 && n_tiles == 0)) return 0;
     GI_REQUIRE(T > 0 && H > 0 && Hkv > 0 && page_size > 0, "attention_rows: sizes must be positive");
     GI_REQUIRE(H % Hkv == 0, "attention_rows: %d query heads are not a multiple of %d key/value heads", H, Hkv);
     GI_REQUIRE(gi_attention_rows_supported(hd, vd), "attention_rows: head size %d / value size %d is not supported (up to %d / %d)",
@@ -236,6 +588,26 @@ static int gi_attention_rows_impl(const void* q, int q_dtype, int ldq, const voi
     a.H = H; a.Hkv = Hkv; a.hd = hd; a.vd = vd; a.v_row = v_row; a.page_size = page_size;
     a.scale = scale; a.window = window; a.chunk = chunk; a.slopes = slopes; a.sinks = sinks;
     a.alias = values_in_keys ? 1 : 0;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    // bfloat16 cache and sizes in whole MMA tiles: the tensor-core form (tiles of rows from the caller's list, or a row each)
+    const int tile_tokens = cache_dtype == kBF16 && ldo % 2 == 0 ? gi_attention_rows_tile_tokens(H, Hkv, hd, vd, values_in_keys) : 0;
+    GI_REQUIRE(list_kind == 0 || tile_tokens > 0, "attention_rows: lists of tiles are for the tensor-core form, which does not serve these sizes");
+    if (tile_tokens > 0 && (list_kind != 0 || group >= 8)) {
+        RowTiles rt;
+        rt.list = tile_list; rt.kind = list_kind;
+        rt.head_blocks = (group + kMmaHeads - 1) / kMmaHeads;
+        rt.splits = splits > 1 ? splits : 1;
+        rt.workspace = workspace;
+        const int tiles = list_kind == 0 ? T : n_tiles;
+        GI_REQUIRE(list_kind == 0 || tile_list != nullptr, "attention_rows: the list of tiles is missing");
+        GI_REQUIRE(rt.splits == 1 || (workspace != nullptr && static_cast<long long>(tiles) * Hkv * rt.head_blocks * rt.splits * kMmaHeads * (vd + 2) <= workspace_floats),
+                   "attention_rows: the workspace of the key ranges is missing or too small");
+        GI_REQUIRE(rt.head_blocks * rt.splits <= 65535, "attention_rows: too many blocks of heads and ranges of keys");
+        const size_t smem_mma = rows_mma_smem(hd, vd, a.alias != 0);
+        if (vd <= 128) return launch_rows_mma<4>(a, rt, tiles, smem_mma, st);
+        if (vd <= 256) return launch_rows_mma<8>(a, rt, tiles, smem_mma, st);
+        return launch_rows_mma<16>(a, rt, tiles, smem_mma, st);
+    }
     // rows of the key tile: pairs of values are read by 32 lanes from 32 rows, free of bank conflicts when the row
     // length counted in pairs is odd
     const int hdp = (hd + 1) & ~1;
@@ -250,9 +622,6 @@ static int gi_attention_rows_impl(const void* q, int q_dtype, int ldq, const voi
                         (a.alias ? 0 : static_cast<size_t>(kRowsTile) * vd * esz);
     GI_REQUIRE(smem <= 200 * 1024, "attention_rows: head size %d with %d heads per block needs %zu bytes of shared memory", hd,
                a.heads_per_block, smem);
-    cudaStream_t st = static_cast<cudaStream_t>(stream);
-    const int rows_left = T;
-    GI_REQUIRE(rows_left <= 2147483647, "attention_rows: too many rows");
     if (cache_dtype == kF32)
         return hpw == 1 ? launch_rows_vi<float, 1>(a, T, blocks_z, warps, smem, st) : launch_rows_vi<float, 4>(a, T, blocks_z, warps, smem, st);
     return hpw == 1 ? launch_rows_vi<__nv_bfloat16, 1>(a, T, blocks_z, warps, smem, st)
@@ -263,8 +632,9 @@ extern "C" int gi_attention_rows(const void* q, int q_dtype, int ldq, const void
                                  void* out, int out_dtype, int ldo, const int* row_req, const int* positions,
                                  const int* block_tables, int table_stride, int T, int H, int Hkv, int hd, int vd, int v_row,
                                  int values_in_keys, int page_size, float scale, int window, int chunk, const float* slopes,
-                                 const float* sinks, void* stream) {
+                                 const float* sinks, const int* tile_list, int list_kind, int n_tiles, int splits, float* workspace,
+                                 long long workspace_floats, void* stream) {
     return gi::dispatch(gi_attention_rows_impl, q, q_dtype, ldq, k_cache, v_cache, cache_dtype, out, out_dtype, ldo, row_req,
                         positions, block_tables, table_stride, T, H, Hkv, hd, vd, v_row, values_in_keys, page_size, scale, window,
-                        chunk, slopes, sinks, stream);
+                        chunk, slopes, sinks, tile_list, list_kind, n_tiles, splits, workspace, workspace_floats, stream);
 }

@@ -140,6 +140,110 @@ grouped_product_kernel(const GroupedArgs p) {
     }
 }
 
+// The same products for few rows (decoding): the weights are what takes the time, so a warp streams whole rows of a
+// group's matrix with 16-byte loads, four rows after one another, and multiplies each with every row of the tile (at most
+// 16, read through the cache); a block of eight warps covers 32 output rows, so a matrix of a few thousand rows is spread
+// over more than a hundred blocks per tile. An output element is the sum of its lanes' partial sums (lane l takes the
+// pieces l, l + 32, ...), added by a fixed xor tree: it depends on its own row only.
+constexpr int kGrRows = 32;           // output rows per block
+
+template <typename T> struct Vec16;
+template <> struct Vec16<float> {
+    static constexpr int N = 4;
+    static __device__ __forceinline__ void load(const float* p, float (&v)[8]) {
+        const float4 x = *reinterpret_cast<const float4*>(p);
+        v[0] = x.x; v[1] = x.y; v[2] = x.z; v[3] = x.w;
+    }
+};
+template <> struct Vec16<__nv_bfloat16> {
+    static constexpr int N = 8;
+    static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&v)[8]) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(p);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(h[i]); v[2 * i] = f.x; v[2 * i + 1] = f.y; }
+    }
+};
+
+// PIECE: values per step of a lane = the weights' 16 bytes (8 bfloat16 or 4 floats); the inputs are read in as many.
+template <typename TA, typename TW, bool GATED>
+__global__ void __launch_bounds__(256)
+grouped_rows_kernel(const GroupedArgs p) {
+    pdl_prologue();
+    constexpr int PIECE = Vec16<TW>::N;
+    __shared__ int s_row[kGpTM];
+    __shared__ int s_count;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    int g;
+    if (p.tile_group) {
+        if (static_cast<int>(blockIdx.x) >= *p.n_tiles) return;
+        g = p.tile_group[blockIdx.x];
+    } else {
+        g = blockIdx.x % p.groups;
+    }
+    if (tid == 0) {             // the tile's rows, the empty places left out
+        int n = 0;
+        for (int i = 0; i < kGpTM; ++i) {
+            int r;
+            if (p.tile_group) r = p.sorted_rows[blockIdx.x * kGpTM + i];
+            else { r = (blockIdx.x / p.groups) * kGpTM + i; if (r >= p.rows) r = -1; }
+            if (r >= 0) s_row[n++] = r;
+        }
+        s_count = n;
+    }
+    __syncthreads();
+    const int m_count = s_count;
+    const TA* A = static_cast<const TA*>(p.a) + p.a_off + static_cast<size_t>(g) * p.a_gs;
+    const TW* W = static_cast<const TW*>(p.w) + static_cast<size_t>(g) * p.w_gs;
+    const int pieces = p.K / PIECE;
+    for (int rr = 0; rr < kGrRows / 8; ++rr) {
+        const int n = blockIdx.y * kGrRows + rr * 8 + warp;
+        if (n >= p.N) break;
+        const TW* wrow = W + static_cast<size_t>(n) * p.ldw;
+        float acc[kGpTM], acc_up[GATED ? kGpTM : 1];
+#pragma unroll
+        for (int i = 0; i < kGpTM; ++i) { acc[i] = 0.f; if (GATED) acc_up[GATED ? i : 0] = 0.f; }
+        for (int c = lane; c < pieces; c += 32) {
+            float wv[8], uv[8];
+            Vec16<TW>::load(wrow + c * PIECE, wv);
+            if (GATED) Vec16<TW>::load(wrow + p.up_off + c * PIECE, uv);
+#pragma unroll
+            for (int i = 0; i < kGpTM; ++i) {
+                if (i < m_count) {
+                    const TA* arow = A + static_cast<size_t>(s_row[i] / p.a_div) * p.lda + c * PIECE;
+                    float av[8];
+                    if (sizeof(TA) == 4 && PIECE == 8) {          // 32-bit inputs against bfloat16 weights: two loads
+                        float lo4[8], hi4[8];
+                        Vec16<float>::load(reinterpret_cast<const float*>(arow), lo4);
+                        Vec16<float>::load(reinterpret_cast<const float*>(arow) + 4, hi4);
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) { av[j] = lo4[j]; av[4 + j] = hi4[j]; }
+                    } else {
+                        Vec16<TA>::load(arow, av);
+                    }
+#pragma unroll
+                    for (int j = 0; j < PIECE; ++j) {
+                        acc[i] = fmaf(av[j], wv[j], acc[i]);
+                        if (GATED) acc_up[GATED ? i : 0] = fmaf(av[j], uv[j], acc_up[GATED ? i : 0]);
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < kGpTM; ++i) {
+            if (i < m_count) {
+                float v = warp_sum(acc[i]);
+                if (GATED) v = gp_act(v, p.act) * warp_sum(acc_up[GATED ? i : 0]);
+                if (lane == 0) {
+                    const size_t o = static_cast<size_t>(s_row[i]) * p.ldo + p.o_off + static_cast<size_t>(g) * p.o_gs + n;
+                    if (p.out_is_f32) static_cast<float*>(p.out)[o] = v;
+                    else static_cast<__nv_bfloat16*>(p.out)[o] = __float2bfloat16_rn(v);
+                }
+            }
+        }
+    }
+}
+
 // ------------------------------------------------------------------------------------------------ routing
 constexpr int kRouteMaxExperts = 1024;
 
@@ -258,6 +362,27 @@ route_combine_kernel(const float* __restrict__ part, const float* __restrict__ w
     y[i] = v;
 }
 
+// Whether every 16-byte load of the few-row form is aligned: pieces of the weights' rows and of the inputs' rows.
+static bool rows_form_fits(const GroupedArgs& p, int a_dtype, int w_dtype) {
+    const int piece = w_dtype == kBF16 ? 8 : 4;
+    const size_t a_size = a_dtype == kBF16 ? 2 : 4, w_size = w_dtype == kBF16 ? 2 : 4;
+    if (a_dtype == kBF16 && w_dtype == kF32) return false;
+    if (p.K % piece || p.ldw % piece || p.w_gs % piece || p.up_off % piece) return false;
+    if (reinterpret_cast<uintptr_t>(p.w) % 16 || reinterpret_cast<uintptr_t>(p.a) % 16) return false;
+    const int a_piece = static_cast<int>(16 / a_size);
+    (void)w_size;
+    return p.lda % a_piece == 0 && p.a_off % a_piece == 0 && p.a_gs % a_piece == 0;
+}
+
+template <bool GATED>
+static int launch_grouped_rows(const GroupedArgs& p, int a_dtype, int w_dtype, unsigned tiles, cudaStream_t st) {
+    dim3 grid(tiles, (p.N + kGrRows - 1) / kGrRows);
+    if (a_dtype == kF32 && w_dtype == kF32) launch_kernel((grouped_rows_kernel<float, float, GATED>), grid, dim3(256), 0, st, p);
+    else if (a_dtype == kF32 && w_dtype == kBF16) launch_kernel((grouped_rows_kernel<float, __nv_bfloat16, GATED>), grid, dim3(256), 0, st, p);
+    else launch_kernel((grouped_rows_kernel<__nv_bfloat16, __nv_bfloat16, GATED>), grid, dim3(256), 0, st, p);
+    return check_launch("grouped_product (rows)");
+}
+
 template <bool GATED>
 static int launch_grouped(const GroupedArgs& p, int a_dtype, int w_dtype, dim3 grid, cudaStream_t st) {
     if (a_dtype == kF32 && w_dtype == kF32) launch_kernel((grouped_product_kernel<float, float, GATED>), grid, dim3(128), 0, st, p);
@@ -289,6 +414,9 @@ static int gi_head_product_impl(const void* a, int a_dtype, long long lda, int a
     const long long tiles = static_cast<long long>((rows + kGpTM - 1) / kGpTM) * heads;
     GI_REQUIRE(tiles <= 2147483647LL, "head_product: too many tiles");
     dim3 grid(static_cast<unsigned>(tiles), (N + kGpTN - 1) / kGpTN);
+    // few tokens: the heads' matrices are what is read; the rotated tail stays with the tiled form
+    if (rows <= 2 * kGpTM && tail == 0 && rows_form_fits(p, a_dtype, w_dtype))
+        return launch_grouped_rows<false>(p, a_dtype, w_dtype, static_cast<unsigned>(tiles), static_cast<cudaStream_t>(stream));
     return launch_grouped<false>(p, a_dtype, w_dtype, grid, static_cast<cudaStream_t>(stream));
 }
 
@@ -308,6 +436,8 @@ static int gi_expert_product_impl(const void* a, int a_dtype, long long lda, int
     p.tile_group = tile_group; p.sorted_rows = sorted_rows; p.n_tiles = n_tiles; p.act = act;
     dim3 grid(max_tiles, (N + kGpTN - 1) / kGpTN);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (rows_form_fits(p, a_dtype, w_dtype))
+        return gated ? launch_grouped_rows<true>(p, a_dtype, w_dtype, max_tiles, st) : launch_grouped_rows<false>(p, a_dtype, w_dtype, max_tiles, st);
     return gated ? launch_grouped<true>(p, a_dtype, w_dtype, grid, st) : launch_grouped<false>(p, a_dtype, w_dtype, grid, st);
 }
 

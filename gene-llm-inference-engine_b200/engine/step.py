@@ -56,6 +56,7 @@ class StepContext:
         self.page_size = engine.page_size
         self.max_requests = engine.max_requests
         self.max_step_tokens = engine.max_step_tokens
+        self.max_position = engine.model.max_position
         self.max_logit_rows = engine.max_logit_rows
         self.compute_dtype = engine.model.dtype
         self.tokens = views["tokens"]

@@ -301,15 +301,58 @@ def attention_rows_supported(head_dim: int, value_dim: int) -> bool:
     return bool(lib().gi_attention_rows_supported(int(head_dim), int(value_dim)))
 
 
+def attention_rows_tensor_cores(on: Optional[bool] = None) -> bool:
+    """With a bfloat16 cache, at least eight query heads to a key/value head, a head size in whole 16s and a value size in
+    whole 64s the row-form attention runs on the tensor cores; ``on`` False makes the CUDA-core form run there too (for
+    comparisons). Returns the old setting."""
+    old = bool(lib().gi_attention_rows_set_mma(1))
+    lib().gi_attention_rows_set_mma(int(old if on is None else on))
+    return old
+
+
+def attention_rows_tile_tokens(num_heads: int, num_kv_heads: int, head_dim: int, value_dim: int, values_in_keys: bool) -> int:
+    """How many consecutive tokens of one request share a tile of the tensor-core form of ``attention_rows`` over a
+    bfloat16 cache (16 // heads per key/value head, at least 1); 0 when that form does not serve these sizes."""
+    return int(lib().gi_attention_rows_tile_tokens(num_heads, num_kv_heads, head_dim, value_dim, int(values_in_keys)))
+
+
+_ROWS_BLOCKS = 296          # about two blocks an SM: what the ranges of keys of a small launch are to fill
+
+
+def attention_rows_splits(n_tiles: int, num_heads: int, num_kv_heads: int, span: int) -> int:
+    """Into how many ranges the keys of every tile of a launch of ``n_tiles`` tiles are cut (1: none): few tiles
+    (decoding) with many keys to see would leave most SMs idle. ``span``: the most keys a row sees."""
+    blocks = n_tiles * num_kv_heads * ((num_heads // num_kv_heads + 15) // 16)
+    if blocks <= 0 or blocks >= sm_count():
+        return 1
+    return max(1, min(16, _ROWS_BLOCKS // blocks, (span + 63) // 64))
+
+
+def attention_rows_workspace_rows(n_tiles: int, num_heads: int, num_kv_heads: int, splits: int) -> int:
+    """Rows [value_dim + 2] of 32-bit workspace that a launch cut into ``splits`` ranges of keys needs."""
+    return n_tiles * num_kv_heads * ((num_heads // num_kv_heads + 15) // 16) * splits * 16 if splits > 1 else 0
+
+
 def attention_rows(q: torch.Tensor, k_cache: torch.Tensor, v_cache: Optional[torch.Tensor], out: torch.Tensor,
                    row_req: torch.Tensor, positions: torch.Tensor, block_tables: torch.Tensor, num_heads: int,
                    num_kv_heads: int, head_dim: int, value_dim: int, page_size: int, scale: float,
                    window: Optional[int] = None, chunk: Optional[int] = None, slopes: Optional[torch.Tensor] = None,
-                   sinks: Optional[torch.Tensor] = None) -> None:
+                   sinks: Optional[torch.Tensor] = None, rows: Optional[torch.Tensor] = None,
+                   tiles: Optional[torch.Tensor] = None, splits: int = 1, workspace: Optional[torch.Tensor] = None) -> None:
     """Attention of every row of ``q`` [T, H*hd] (32-bit or bfloat16) over its request's pages, 32-bit arithmetic.
     ``v_cache`` None: the values are the first ``value_dim`` columns of the key rows. ``window``: the last w positions;
     ``chunk``: only keys of the query's own block of c positions; ``slopes`` [H]: slope_h * distance is taken off a
-    score; ``sinks`` [H]: exp(sinks_h) more in the softmax's denominator. ``out`` [T, H*vd], 32-bit or bfloat16."""
+    score; ``sinks`` [H]: exp(sinks_h) more in the softmax's denominator. ``out`` [T, H*vd], 32-bit or bfloat16.
+    (See attention_rows_tensor_cores for the form that rounds queries and softmax weights to bfloat16.)
+    Tensor-core form only (attention_rows_tile_tokens() > 0): ``rows`` [n] lists the step rows to work on, a tile each;
+    ``tiles`` [m, 3] = (first row, tokens (at most attention_rows_tile_tokens()), request) lists tiles of consecutive
+    tokens of one request; ``splits`` > 1 cuts every tile's keys into ranges that run side by side and meet in
+    ``workspace`` (attention_rows_workspace_rows() rows of value_dim + 2 floats)."""
+    if rows is not None and tiles is not None:
+        raise KernelError("attention_rows: give rows or tiles, not both")
+    lst, kind, n_list = (rows, 1, rows.numel()) if rows is not None else (tiles, 2, tiles.shape[0]) if tiles is not None else (None, 0, 0)
+    if tiles is not None and (tiles.dim() != 2 or tiles.shape[1] != 3):
+        raise KernelError("attention_rows: tiles must be [m, 3]")
     T = q.shape[0]
     if q.dim() != 2 or q.shape[1] != num_heads * head_dim or out.shape != (T, num_heads * value_dim):
         raise KernelError("attention_rows: q must be [T, H*hd] and out [T, H*vd]")
@@ -326,7 +369,48 @@ def attention_rows(q: torch.Tensor, k_cache: torch.Tensor, v_cache: Optional[tor
         _dev(positions, "positions", torch.int32), _dev(block_tables, "block_tables", torch.int32), block_tables.shape[1], T,
         num_heads, num_kv_heads, head_dim, value_dim, head_dim if v_cache is None else value_dim, int(v_cache is None), page_size,
         float(scale), int(window or 0), int(chunk or 0), _opt(slopes, "slopes", torch.float32), _opt(sinks, "sinks", torch.float32),
-        _stream()), "attention_rows")
+        _opt(lst, "rows or tiles", torch.int32), kind, n_list, int(splits), _opt(workspace, "workspace", torch.float32),
+        0 if workspace is None else workspace.numel(), _stream()), "attention_rows")
+    if splits > 1:
+        count_launches(1)
+
+
+def attention_rows_of_step(ctx, q: torch.Tensor, k_cache: torch.Tensor, v_cache: Optional[torch.Tensor], out: torch.Tensor,
+                           tables: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int, value_dim: int, scale: float,
+                           window: Optional[int], chunk: Optional[int], slopes: Optional[torch.Tensor],
+                           sinks: Optional[torch.Tensor]) -> None:
+    """``attention_rows`` for all rows of a step. Over a bfloat16 cache with sizes that the tensor-core form serves, the
+    step's single tokens and the tiles of its prompt portions (``ctx.attention_work``) run as two launches, each with its
+    keys cut into ranges when it has few tiles; otherwise one launch works row by row."""
+    common = dict(window=window, chunk=chunk, slopes=slopes, sinks=sinks)
+    per_tile = attention_rows_tile_tokens(num_heads, num_kv_heads, head_dim, value_dim, v_cache is None) \
+        if k_cache.dtype is torch.bfloat16 else 0
+    if per_tile == 0 or not hasattr(ctx, "attention_work"):
+        attention_rows(q, k_cache, v_cache, out, ctx.row_req, ctx.positions, tables, num_heads, num_kv_heads, head_dim, value_dim,
+                       ctx.page_size, scale, **common)
+        return
+    rows, work, _ = ctx.attention_work(per_tile)
+    span = min(v for v in (window, chunk, getattr(ctx, "max_position", None), 1 << 30) if v)
+    for name, lst, n in (("rows", rows, rows.numel()), ("tiles", work, work.shape[0])):
+        if n == 0:
+            continue
+        splits = attention_rows_splits(n, num_heads, num_kv_heads, span)
+        ws = None
+        if splits > 1:
+            ws = ctx.scratch("attention_rows_ranges_" + name, (attention_rows_workspace_rows(n, num_heads, num_kv_heads, splits), value_dim + 2),
+                             torch.float32, capacity=(_ROWS_BLOCKS + 16) * 16)
+        attention_rows(q, k_cache, v_cache, out, ctx.row_req, ctx.positions, tables, num_heads, num_kv_heads, head_dim, value_dim,
+                       ctx.page_size, scale, splits=splits, workspace=ws, **{name: lst}, **common)
+
+
+def attention_rows_launch_key(ctx, num_heads: int, num_kv_heads: int, head_dim: int, value_dim: int, values_in_keys: bool,
+                              dtype: torch.dtype):
+    """What the launches of ``attention_rows_of_step`` depend on besides the token count."""
+    per_tile = attention_rows_tile_tokens(num_heads, num_kv_heads, head_dim, value_dim, values_in_keys) if dtype is torch.bfloat16 else 0
+    if per_tile == 0 or not hasattr(ctx, "attention_work"):
+        return ()
+    rows, work, _ = ctx.attention_work(per_tile)
+    return (rows.numel(), work.shape[0])
 
 
 def head_product(a: torch.Tensor, a_offset: int, a_head_stride: int, w: torch.Tensor, out: torch.Tensor, out_offset: int,

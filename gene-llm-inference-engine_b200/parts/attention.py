@@ -143,6 +143,9 @@ class AttentionMixer:
         """What the mixer's launches depend on besides the token count: whose cache it uses, and (tensor-core
         kernels) how many rows are single decoded tokens, how many tiles the prompt portions make and how many
         chunks the longest context of a single token has. Asking also places this step's work lists on the device."""
+        if self.row_form:
+            return (run.cache_layer, run.writes_cache) + kernels.attention_rows_launch_key(
+                ctx, self.num_heads, self.num_kv_heads, self.head_dim, self.value_dim, False, self.dtype)
         if not self._fast_now(ctx):
             return (run.cache_layer, run.writes_cache)
         rows, work, longest = ctx.attention_work(self.prefill_rows(ctx.page_size) // (self.num_heads // self.num_kv_heads))
@@ -223,9 +226,8 @@ class AttentionMixer:
                                 write_kv=run.writes_cache, value_dim=self.value_dim)
         if self.row_form:
             att = ctx.scratch("att", (T, H * self.value_dim), self.dtype)
-            kernels.attention_rows(q, k_cache, v_cache, att, ctx.row_req, ctx.positions, tables, H, Hkv, hd, self.value_dim,
-                                   ctx.page_size, self.scale, window=self.window, chunk=self.chunk, slopes=self.slopes,
-                                   sinks=self.sink_weight)
+            kernels.attention_rows_of_step(ctx, q, k_cache, v_cache, att, tables, H, Hkv, hd, self.value_dim, self.scale,
+                                           self.window, self.chunk, self.slopes, self.sink_weight)
             self.w_o.forward(att, x, accumulate=True, then=then)
             return
         att = ctx.scratch("att", (T, H * hd), self.dtype)

@@ -79,7 +79,8 @@ class LatentAttentionMixer:
         return None
 
     def launch_key(self, ctx, run):
-        return (run.cache_layer, run.writes_cache)
+        H, kr, r = self.num_heads, self.kv_rank, self.rotary_dim
+        return (run.cache_layer, run.writes_cache) + kernels.attention_rows_launch_key(ctx, H, 1, kr + r, kr, True, self.dtype)
 
     def forward(self, ctx, run, xn: torch.Tensor, x: torch.Tensor, then=None) -> None:
         T = xn.shape[0]
@@ -98,8 +99,8 @@ class LatentAttentionMixer:
         kernels.head_product(q, 0, d + r, self.w_uk_t, qa, 0, kr + r, tail=r, freq=self.freq, amplitude=self.amplitude,
                              positions=ctx.positions)
         ol = ctx.scratch("latent_out", (T, H * kr), torch.float32)
-        kernels.attention_rows(qa, cache, None, ol, ctx.row_req, ctx.positions, tables, H, 1, kr + r, kr, ctx.page_size,
-                               self.scale, window=self.window, sinks=self.sink)
+        kernels.attention_rows_of_step(ctx, qa, cache, None, ol, tables, H, 1, kr + r, kr, self.scale, self.window, None, None,
+                                       self.sink)
         att = ctx.scratch("att", (T, H * dv), self.dtype)
         kernels.head_product(ol, 0, kr, self.w_uv, att, 0, dv)
         self.w_o.forward(att, x, accumulate=True, then=then)

@@ -89,6 +89,10 @@ def _paged(rows, dtype, page_size, seed):
     (9, 1, 36, 28, 21, None, False, True, True),        # values inside the key rows, heads beyond a full group of four
     (20, 1, 136, 136, None, None, False, True, True),   # two blocks of heads, no mask but causality
     (3, 3, 300, 260, 7, None, False, False, False),     # long heads
+    (16, 1, 80, 64, 29, None, False, True, True),       # bfloat16: the tensor-core form (a latent of 64 + 16)
+    (24, 1, 144, 128, None, 40, True, True, True),      # two blocks of heads, the second half full
+    (16, 2, 32, 64, 50, None, True, False, False),      # eight heads to a key/value head, values in pages of their own
+    (16, 1, 528, 512, 64, None, False, False, True),    # the widest value
 ])
 def test_attention_rows(dtype, H, Hkv, hd, vd, window, chunk, biased, sunk, alias):
     from geneinfer_b200.ops import kernels
@@ -120,23 +124,93 @@ def test_attention_rows(dtype, H, Hkv, hd, vd, window, chunk, biased, sunk, alia
                                torch.zeros(len(rows), dtype=torch.int32, device=DEV), rows.to(DEV), table, H, Hkv, hd, vd, page,
                                0.21, window=window, chunk=chunk, slopes=None if slopes is None else slopes.to(DEV),
                                sinks=None if sinks is None else sinks.to(DEV))
-        exact = q_dtype is torch.float32 and out_dtype is torch.float32
-        _close(out.cpu().float(), want[rows.long()], torch.float32 if exact else torch.bfloat16, "attention rows", f32=3e-6)
+        on_tensor_cores = dtype is torch.bfloat16 and H // Hkv >= 8 and hd % 16 == 0 and vd % 64 == 0
+        exact = q_dtype is torch.float32 and out_dtype is torch.float32 and not on_tensor_cores
+        _close(out.cpu().float(), want[rows.long()], torch.float32 if exact else torch.bfloat16, "attention rows", f32=1e-5)
+        if on_tensor_cores:          # and the CUDA-core form at the same sizes
+            old = kernels.attention_rows_tensor_cores(False)
+            other = torch.full_like(out, float("nan"))
+            kernels.attention_rows(q[rows.long()].reshape(len(rows), H * hd).to(DEV).to(q_dtype), k_pages, v_pages, other,
+                                   torch.zeros(len(rows), dtype=torch.int32, device=DEV), rows.to(DEV), table, H, Hkv, hd, vd, page,
+                                   0.21, window=window, chunk=chunk, slopes=None if slopes is None else slopes.to(DEV),
+                                   sinks=None if sinks is None else sinks.to(DEV))
+            kernels.attention_rows_tensor_cores(old)
+            _close(other.cpu().float(), want[rows.long()], torch.float32 if q_dtype is torch.float32 and out_dtype is torch.float32
+                   else torch.bfloat16, "attention rows, CUDA cores", f32=1e-5)
+
+
+@pytest.mark.parametrize("H, Hkv, hd, vd, window, chunk, biased, sunk, alias", [
+    (4, 2, 16, 64, None, 13, True, True, False),        # eight tokens of two heads to a tile; blocks, bias, sinks
+    (16, 1, 80, 64, 29, None, False, True, True),       # a token to a tile: sixteen heads over a latent of 64 + 16
+    (8, 8, 32, 64, 20, None, False, False, False),      # sixteen tokens to a tile
+    (6, 2, 48, 128, 17, 25, True, True, False),         # groups of three: five tokens to a tile and a row left over
+    (40, 1, 144, 128, 64, None, False, True, True),     # three blocks of heads, the last one half full
+])
+def test_attention_rows_in_tiles_and_ranges_of_keys(H, Hkv, hd, vd, window, chunk, biased, sunk, alias):
+    """The tensor-core form over tiles of consecutive tokens (every row with its own first and last key), over listed
+    rows, and with the keys cut into ranges that a second kernel merges: all agree with the plain softmax."""
+    from geneinfer_b200.ops import kernels
+    dtype = torch.bfloat16
+    g = torch.Generator().manual_seed(5)
+    n, page = 150, 16
+    q = torch.randn(n, H, hd, generator=g)
+    k = _bf(torch.randn(n, Hkv, hd, generator=g))
+    v = k[..., :vd] if alias else _bf(torch.randn(n, Hkv, vd, generator=g))
+    slopes = torch.rand(H, generator=g) * 0.3 if biased else None
+    sinks = torch.randn(H, generator=g) * 2 if sunk else None
+    k_pages, table = _paged(k, dtype, page, 2)
+    v_pages = None if alias else _paged(v, dtype, page, 2)[0]
+    pos = torch.arange(n)
+    mask = torch.ones(n, n, dtype=torch.bool).tril()
+    if window:
+        mask &= pg.window_mask(pos, window)
+    if chunk:
+        mask &= pg.chunk_mask(pos, chunk)
+    per = H // Hkv
+    scores = torch.einsum("ihd,jhd->hij", q.double(), k.double().repeat_interleave(per, 1)) * 0.21
+    if biased:
+        scores = scores - slopes.double().view(H, 1, 1) * (pos[:, None] - pos[None, :]).double()[None]
+    p = pg.softmax_rows(scores, mask, None if sinks is None else sinks.double())
+    want = torch.einsum("hij,jhd->ihd", p, v.double().repeat_interleave(per, 1)).reshape(n, H * vd)
+    per_tile = kernels.attention_rows_tile_tokens(H, Hkv, hd, vd, alias)
+    assert per_tile == max(1, 16 // per)
+    # the step: rows 0..n-1 of one request in order; tiles start at an odd row so that they straddle blocks and pages
+    tiles = [(0, 3, 0)] + [(t, min(per_tile, n - t), 0) for t in range(3, n, per_tile)] if per_tile >= 3 else \
+        [(t, min(per_tile, n - t), 0) for t in range(0, n, per_tile)]
+    tiles_d = torch.tensor(tiles, dtype=torch.int32, device=DEV)
+    some = torch.tensor([149, 0, 77, 31, 32, 12, 13], dtype=torch.int32, device=DEV)
+    args = (q.reshape(n, H * hd).to(DEV), k_pages, v_pages)
+    rest = (torch.zeros(n, dtype=torch.int32, device=DEV), pos.int().to(DEV), table, H, Hkv, hd, vd, page, 0.21)
+    kw = dict(window=window, chunk=chunk, slopes=None if slopes is None else slopes.to(DEV), sinks=None if sinks is None else sinks.to(DEV))
+    for splits in (1, 3, 16):
+        ws = None
+        if splits > 1:
+            ws = torch.full((kernels.attention_rows_workspace_rows(len(tiles), H, Hkv, splits), vd + 2), float("nan"), device=DEV)
+        out = torch.full((n, H * vd), float("nan"), device=DEV)
+        kernels.attention_rows(*args, out, *rest, tiles=tiles_d, splits=splits, workspace=ws, **kw)
+        _close(out.cpu(), want, dtype, f"tiles of {per_tile} tokens, {splits} ranges")
+        out2 = torch.full((n, H * vd), float("nan"), device=DEV)
+        ws2 = None if splits == 1 else torch.full((kernels.attention_rows_workspace_rows(len(some), H, Hkv, splits), vd + 2), float("nan"), device=DEV)
+        kernels.attention_rows(*args, out2, *rest, rows=some, splits=splits, workspace=ws2, **kw)
+        _close(out2.cpu()[some.cpu().long()], want[some.cpu().long()], dtype, f"listed rows, {splits} ranges")
+        untouched = torch.ones(n, dtype=torch.bool)
+        untouched[some.cpu().long()] = False
+        assert torch.isnan(out2.cpu()[untouched]).all()
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_head_product_with_a_rotated_tail(dtype):
     from geneinfer_b200.ops import kernels
     g = torch.Generator().manual_seed(4)
-    for T, H, N, K, tail in ((37, 3, 70, 24, 8), (1, 5, 8, 100, 0), (16, 2, 64, 32, 2)):
-        a = torch.randn(T, 5 + H * (K + tail) + 3, generator=g)
+    for T, H, N, K, tail, off in ((37, 3, 70, 24, 8, 5), (1, 5, 8, 100, 0, 5), (16, 2, 64, 32, 2, 5), (3, 4, 40, 64, 0, 8), (20, 2, 33, 48, 0, 16)):
+        a = torch.randn(T, off + H * (K + tail) + 3, generator=g)
         w = _bf(torch.randn(H, N, K, generator=g))
         freq = torch.rand(max(tail // 2, 1), generator=g)[:tail // 2]
         pos = torch.randint(0, 900, (T,), generator=g)
         out = torch.full((T, 2 + H * (N + tail)), float("nan"), dtype=torch.float32, device=DEV)
-        kernels.head_product(a.to(DEV), 5, K + tail, w.to(DEV).to(dtype), out, 2, N + tail, tail=tail,
+        kernels.head_product(a.to(DEV), off, K + tail, w.to(DEV).to(dtype), out, 2, N + tail, tail=tail,
                              freq=freq.to(DEV) if tail else None, amplitude=1.3, positions=pos.int().to(DEV) if tail else None)
-        x = a[:, 5:5 + H * (K + tail)].view(T, H, K + tail).double()
+        x = a[:, off:off + H * (K + tail)].view(T, H, K + tail).double()
         want = torch.einsum("thk,hnk->thn", x[..., :K], w.double())
         got = out.cpu()[:, 2:].view(T, H, N + tail)
         _close(got[..., :N], want, torch.float32, "head product")
