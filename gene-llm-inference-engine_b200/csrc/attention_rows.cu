@@ -94,11 +94,15 @@ attention_rows_kernel(const RowsArgs a) {
     for (int base = lo; base <= pos; base += kRowsTile) {
         const int n_keys = min(kRowsTile, pos - base + 1);
         __syncthreads();                       // the tile before is done with (and the queries are written)
-        // every warp fetches keys of its own: key j of the tile lands in row j
+        // every warp fetches keys of its own: key j of the tile lands in row j (lane j looks up key j's page row, so the
+        // look-ups of a tile are in flight together)
+        size_t my_row = 0;
+        if (lane < n_keys) {
+            const int pl = base + lane;
+            my_row = (static_cast<size_t>(table[pl / a.page_size]) * a.Hkv + g) * a.page_size + (pl % a.page_size);
+        }
         for (int j = warp; j < n_keys; j += blockDim.x >> 5) {
-            const int p = base + j;
-            const int page = table[p / a.page_size];
-            const size_t row = (static_cast<size_t>(page) * a.Hkv + g) * a.page_size + (p % a.page_size);
+            const size_t row = __shfl_sync(0xffffffffu, static_cast<unsigned long long>(my_row), j);
             const T* src = kc + row * a.hd;
             T* dst = s_k + j * a.ks;
             for (int d = lane; d < hdp; d += 32) dst[d] = d < a.hd ? src[d] : from_float<T>(0.f);
@@ -218,8 +222,9 @@ __device__ __forceinline__ uint32_t rows_pack(float lo, float hi) {
 __device__ __forceinline__ uint32_t rows_smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 
 constexpr int kMmaHeads = 16;          // rows of an MMA tile
+constexpr int kMmaOwnRows = 64;        // rows of a block whose warps each own an MMA tile of rows (small heads)
 constexpr int kMmaPad = 8;             // bfloat16 values of padding per row of a tile (16 bytes: ldmatrix without conflicts)
-constexpr int kMmaSStride = kRowsTile + 4;
+constexpr int kMmaSStride = kRowsTile + 8;     // 40 floats: pairs of columns read by half a warp fall into different banks
 
 // Which rows of the step a block works on: tile b of the list.
 struct RowTiles {
@@ -227,13 +232,14 @@ struct RowTiles {
     int kind;
     int head_blocks;       // blocks of sixteen heads per key/value head (groups of more than sixteen heads)
     int splits;            // ranges of keys that run side by side (> 1: results go through ``workspace``)
-    float* workspace;      // [tiles][Hkv][head_blocks][splits][16][vd + 2]
+    int block_rows;        // query rows of a block: 16 (the warps share them) or 64 (a warp owns 16)
+    float* workspace;      // [tiles][Hkv][head_blocks][splits][block_rows][vd + 2]
 };
 
 struct TileRows {
     int row0, ntok, gp;
-    __device__ __forceinline__ int token(int r) const { return gp == kMmaHeads ? 0 : r / gp; }
-    __device__ __forceinline__ int head(int r) const { return gp == kMmaHeads ? r : r % gp; }
+    __device__ __forceinline__ int token(int r) const { return r / gp; }
+    __device__ __forceinline__ int head(int r) const { return r % gp; }
 };
 __device__ __forceinline__ TileRows tile_rows(const RowTiles& rt, int b, int group) {
     TileRows t;
@@ -249,10 +255,13 @@ __device__ __forceinline__ int first_visible(const RowsArgs& a, int pos) {
     return lo;
 }
 
-// NV: 8-wide tiles of value dimensions per warp (vd <= 32 NV).
-template <int NV>
+// NV: 8-wide tiles of value dimensions per warp. OWN false: the four warps share sixteen rows (vd <= 32 NV); OWN true
+// (head and value sizes up to 128, groups of at most sixteen heads): every warp owns sixteen of the block's 64 rows,
+// with all of the head dimension and all value dimensions (vd <= 8 NV), so the warps exchange nothing.
+template <int NV, bool OWN>
 __global__ void __launch_bounds__(128)
 attention_rows_mma_kernel(const RowsArgs a, const RowTiles rt) {
+    constexpr int RT = OWN ? kMmaOwnRows : kMmaHeads;
     pdl_prologue();
     extern __shared__ __align__(16) unsigned char smem_raw[];
     using bf = __nv_bfloat16;
@@ -263,11 +272,11 @@ attention_rows_mma_kernel(const RowsArgs a, const RowTiles rt) {
     const TileRows tr = tile_rows(rt, blockIdx.x, group);
     const int first_head = zb * kMmaHeads;
     const int n_heads = min(kMmaHeads, group - first_head);
-    const int n_rows = tr.gp == kMmaHeads ? n_heads : tr.ntok * tr.gp;
+    const int n_rows = (!OWN && tr.gp == kMmaHeads) ? n_heads : tr.ntok * tr.gp;
     const int qs = a.hd + kMmaPad;                     // row length of the query and key tiles
     const int vs = a.alias ? qs : a.vd + kMmaPad;
     bf* s_q = reinterpret_cast<bf*>(smem_raw);                              // [16][qs]
-    bf* s_k = s_q + kMmaHeads * qs;                                         // [2][32][qs]
+    bf* s_k = s_q + RT * qs;                                                // [2][32][qs]
     bf* s_v = a.alias ? s_k : s_k + 2 * kRowsTile * qs;                     // [2][32][vs]
     float* s_s = reinterpret_cast<float*>(s_k + 2 * kRowsTile * qs + (a.alias ? 0 : 2 * kRowsTile * vs));   // [4][16][36]
 
@@ -283,11 +292,14 @@ attention_rows_mma_kernel(const RowsArgs a, const RowTiles rt) {
 
     auto fetch = [&](int tile, int stage) {
         const int base = lo_t + tile * kRowsTile;
+        // lane j looks up the page row of key j: one load in flight per lane instead of a chain of dependent ones
+        const int pl = base + lane;
+        long long my_row = -1;
+        if (pl <= hi_t) my_row = (static_cast<long long>(table[pl / a.page_size]) * a.Hkv + g) * a.page_size + (pl % a.page_size);
         for (int j = warp; j < kRowsTile; j += 4) {
-            const int p = base + j;
-            const bool in = p <= hi_t;
-            size_t row = 0;
-            if (in) row = (static_cast<size_t>(table[p / a.page_size]) * a.Hkv + g) * a.page_size + (p % a.page_size);
+            const long long rj = __shfl_sync(0xffffffffu, my_row, j);
+            const bool in = rj >= 0;
+            const size_t row = in ? static_cast<size_t>(rj) : 0;
             const bf* src = kc + row * a.hd;
             const uint32_t dst = rows_smem_u32(s_k + (stage * kRowsTile + j) * qs);
             for (int c = lane; c < k_chunks; c += 32) rows_cp_async16(dst + c * 16, src + c * 8, in ? 16 : 0);   // 0 bytes: zeros
@@ -301,18 +313,36 @@ attention_rows_mma_kernel(const RowsArgs a, const RowTiles rt) {
     };
 
     if (it0 < it1) fetch(it0, 0);
-    for (int i = threadIdx.x; i < kMmaHeads * a.hd; i += 128) {
-        const int r = i / a.hd, d = i % a.hd;
-        float v = 0.f;
-        if (r < n_rows) {
-            const size_t off = static_cast<size_t>(tr.row0 + tr.token(r)) * a.ldq +
-                               static_cast<size_t>(g * group + first_head + tr.head(r)) * a.hd + d;
-            v = a.q_is_f32 ? static_cast<const float*>(a.q)[off] : to_float(static_cast<const bf*>(a.q)[off]);
+    // the queries, a warp per row: 16-byte loads where the rows allow them
+    for (int r = warp; r < RT; r += 4) {
+        bf* dst = s_q + r * qs;
+        if (r >= n_rows) {
+            for (int d = lane; d < a.hd; d += 32) dst[d] = __float2bfloat16_rn(0.f);
+            continue;
         }
-        s_q[r * qs + d] = __float2bfloat16_rn(v);
+        const size_t off = static_cast<size_t>(tr.row0 + tr.token(r)) * a.ldq + static_cast<size_t>(g * group + first_head + tr.head(r)) * a.hd;
+        if (a.q_is_f32) {
+            const float* src = static_cast<const float*>(a.q) + off;
+            if (a.ldq % 4 == 0 && reinterpret_cast<uintptr_t>(a.q) % 16 == 0) {
+                for (int d = lane * 4; d < a.hd; d += 128) {
+                    const float4 v = *reinterpret_cast<const float4*>(src + d);
+                    *reinterpret_cast<uint2*>(dst + d) = make_uint2(rows_pack(v.x, v.y), rows_pack(v.z, v.w));
+                }
+            } else {
+                for (int d = lane; d < a.hd; d += 32) dst[d] = __float2bfloat16_rn(src[d]);
+            }
+        } else {
+            const bf* src = static_cast<const bf*>(a.q) + off;
+            if (a.ldq % 8 == 0 && reinterpret_cast<uintptr_t>(a.q) % 16 == 0) {
+                for (int d = lane * 8; d < a.hd; d += 256) *reinterpret_cast<uint4*>(dst + d) = *reinterpret_cast<const uint4*>(src + d);
+            } else {
+                for (int d = lane; d < a.hd; d += 32) dst[d] = src[d];
+            }
+        }
     }
 
     const int gr = lane >> 2, tq = lane & 3;            // the fragment's rows gr and gr + 8 and its pair of columns
+    const int rb = OWN ? warp * kMmaHeads : 0;          // the first of this warp's sixteen rows
     float o[NV][4];
 #pragma unroll
     for (int i = 0; i < NV; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
@@ -320,14 +350,15 @@ attention_rows_mma_kernel(const RowsArgs a, const RowTiles rt) {
     int pos_r[2], lo_r[2];
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
-        const int r = gr + 8 * h;
+        const int r = rb + gr + 8 * h;
         const bool row_on = r < n_rows;
         pos_r[h] = row_on ? pos0 + tr.token(r) : -1;              // a row that is not there sees no key
         lo_r[h] = row_on ? first_visible(a, pos_r[h]) : 0;
         if (a.slopes && row_on) slope[h] = a.slopes[g * group + first_head + tr.head(r)];
     }
-    const int nv = a.vd / 32;                            // 8-wide value tiles of this warp
-    const int v0 = warp * (a.vd / 4);                    // its first value dimension
+    const int nv = OWN ? a.vd / 8 : a.vd / 32;           // 8-wide value tiles of this warp
+    const int v0 = OWN ? 0 : warp * (a.vd / 4);          // its first value dimension
+    const bool warp_on = !OWN || rb < n_rows;            // (a warp without rows only helps to fetch)
     const int k_steps = a.hd / 16;
 
     for (int it = it0; it < it1; ++it) {
@@ -341,37 +372,52 @@ attention_rows_mma_kernel(const RowsArgs a, const RowTiles rt) {
         float s[4][4];
 #pragma unroll
         for (int i = 0; i < 4; ++i) { s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f; }
-        for (int ks = warp; ks < k_steps; ks += 4) {
-            uint32_t qa[4];
-            rows_ldsm_x4(rows_smem_u32(s_q + (lane & 15) * qs + ks * 16 + (lane >> 4) * 8), qa[0], qa[1], qa[2], qa[3]);
+        const uint32_t q_addr = rows_smem_u32(s_q + (rb + (lane & 15)) * qs + (lane >> 4) * 8);
+        const uint32_t k_addr = rows_smem_u32(kt + ((lane >> 4) * 8 + (lane & 7)) * qs + ((lane >> 3) & 1) * 8);
+        if (warp_on) {
+            for (int ks = OWN ? 0 : warp; ks < k_steps; ks += OWN ? 1 : 4) {
+                uint32_t qa[4];
+                rows_ldsm_x4(q_addr + ks * 32, qa[0], qa[1], qa[2], qa[3]);
 #pragma unroll
-            for (int half = 0; half < 2; ++half) {
-                uint32_t b0, b1, b2, b3;
-                rows_ldsm_x4(rows_smem_u32(kt + (half * 16 + (lane >> 4) * 8 + (lane & 7)) * qs + ks * 16 + ((lane >> 3) & 1) * 8), b0, b1, b2, b3);
-                rows_mma(s[half * 2], qa, b0, b1);
-                rows_mma(s[half * 2 + 1], qa, b2, b3);
+                for (int half = 0; half < 2; ++half) {
+                    uint32_t b0, b1, b2, b3;
+                    rows_ldsm_x4(k_addr + half * 16 * qs * 2 + ks * 32, b0, b1, b2, b3);
+                    rows_mma(s[half * 2], qa, b0, b1);
+                    rows_mma(s[half * 2 + 1], qa, b2, b3);
+                }
             }
         }
-        float* mine = s_s + warp * kMmaHeads * kMmaSStride;
+        if (!OWN) {
+            float* mine = s_s + warp * kMmaHeads * kMmaSStride;
 #pragma unroll
-        for (int nt = 0; nt < 4; ++nt) {
-            mine[gr * kMmaSStride + nt * 8 + 2 * tq] = s[nt][0];
-            mine[gr * kMmaSStride + nt * 8 + 2 * tq + 1] = s[nt][1];
-            mine[(gr + 8) * kMmaSStride + nt * 8 + 2 * tq] = s[nt][2];
-            mine[(gr + 8) * kMmaSStride + nt * 8 + 2 * tq + 1] = s[nt][3];
+            for (int nt = 0; nt < 4; ++nt) {
+                *reinterpret_cast<float2*>(mine + gr * kMmaSStride + nt * 8 + 2 * tq) = make_float2(s[nt][0], s[nt][1]);
+                *reinterpret_cast<float2*>(mine + (gr + 8) * kMmaSStride + nt * 8 + 2 * tq) = make_float2(s[nt][2], s[nt][3]);
+            }
+            __syncthreads();
         }
-        __syncthreads();
+        if (!warp_on) continue;
         // every warp adds the four partial sums in warp order and takes the softmax step of all sixteen rows
         const int base = lo_t + it * kRowsTile;
         float tile_max[2] = {-INFINITY, -INFINITY};
 #pragma unroll
         for (int nt = 0; nt < 4; ++nt) {
+            if (!OWN) {
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    float2 sum2 = make_float2(0.f, 0.f);
+#pragma unroll
+                    for (int w = 0; w < 4; ++w) {
+                        const float2 part = *reinterpret_cast<const float2*>(s_s + (w * kMmaHeads + gr + 8 * h) * kMmaSStride + nt * 8 + 2 * tq);
+                        sum2.x += part.x; sum2.y += part.y;
+                    }
+                    s[nt][2 * h] = sum2.x; s[nt][2 * h + 1] = sum2.y;
+                }
+            }
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-                const int h = e >> 1, r = gr + h * 8, col = nt * 8 + 2 * tq + (e & 1);
-                float v = 0.f;
-#pragma unroll
-                for (int w = 0; w < 4; ++w) v += s_s[(w * kMmaHeads + r) * kMmaSStride + col];
+                const int h = e >> 1, col = nt * 8 + 2 * tq + (e & 1);
+                float v = s[nt][e];
                 const int key = base + col;
                 v = (key >= lo_r[h] && key <= pos_r[h]) ? v * a.scale - slope[h] * static_cast<float>(pos_r[h] - key) : -INFINITY;
                 s[nt][e] = v;
@@ -409,12 +455,12 @@ attention_rows_mma_kernel(const RowsArgs a, const RowTiles rt) {
         for (int ks = 0; ks < 2; ++ks) {
             uint32_t pa[4] = {rows_pack(s[2 * ks][0], s[2 * ks][1]), rows_pack(s[2 * ks][2], s[2 * ks][3]),
                               rows_pack(s[2 * ks + 1][0], s[2 * ks + 1][1]), rows_pack(s[2 * ks + 1][2], s[2 * ks + 1][3])};
+            const uint32_t v_addr = rows_smem_u32(vt + (ks * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * vs + v0 + (lane >> 4) * 8);
 #pragma unroll
             for (int np = 0; np < NV / 2; ++np) {
                 if (2 * np < nv) {
                     uint32_t b0, b1, b2, b3;
-                    rows_ldsm_x4_trans(rows_smem_u32(vt + (ks * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * vs + v0 + np * 16 + (lane >> 4) * 8),
-                                       b0, b1, b2, b3);
+                    rows_ldsm_x4_trans(v_addr + np * 32, b0, b1, b2, b3);
                     rows_mma(o[2 * np], pa, b0, b1);
                     rows_mma(o[2 * np + 1], pa, b2, b3);
                 }
@@ -425,21 +471,21 @@ attention_rows_mma_kernel(const RowsArgs a, const RowTiles rt) {
 
     if (rt.splits > 1) {
         // this range's unnormalised sums, maximum and weight: merged by attention_rows_merge_kernel
-        float* ws = rt.workspace + ((((static_cast<size_t>(blockIdx.x) * a.Hkv + g) * rt.head_blocks + zb) * rt.splits + split) * kMmaHeads) * (a.vd + 2);
+        float* ws = rt.workspace + ((((static_cast<size_t>(blockIdx.x) * a.Hkv + g) * rt.head_blocks + zb) * rt.splits + split) * RT) * (a.vd + 2);
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
-            float* row = ws + static_cast<size_t>(gr + 8 * h) * (a.vd + 2);
+            float* row = ws + static_cast<size_t>(rb + gr + 8 * h) * (a.vd + 2);
 #pragma unroll
             for (int i = 0; i < NV; ++i) {
                 if (i < nv) { row[v0 + i * 8 + 2 * tq] = o[i][2 * h]; row[v0 + i * 8 + 2 * tq + 1] = o[i][2 * h + 1]; }
             }
-            if (warp == 0 && tq == 0) { row[a.vd] = m[h]; row[a.vd + 1] = l[h]; }
+            if ((OWN || warp == 0) && tq == 0) { row[a.vd] = m[h]; row[a.vd + 1] = l[h]; }
         }
         return;
     }
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
-        const int r = gr + 8 * h;
+        const int r = rb + gr + 8 * h;
         if (r >= n_rows) continue;
         const int head = g * group + first_head + tr.head(r);
         float M = m[h], L = l[h], f = 1.f;
@@ -462,45 +508,50 @@ attention_rows_mma_kernel(const RowsArgs a, const RowTiles rt) {
     }
 }
 
-// Merges the ranges of keys of a tile, in their order: one block per (tile, key/value head, block of heads), a warp per row.
+// Merges the ranges of keys of a tile, in their order: one block per (tile, key/value head and block of heads, row).
 __global__ void __launch_bounds__(128)
 attention_rows_merge_kernel(const RowsArgs a, const RowTiles rt) {
     pdl_prologue();
-    const int g = blockIdx.y, zb = blockIdx.z;
+    __shared__ float s_w[16];
+    __shared__ float s_inv;
+    const int g = blockIdx.y / rt.head_blocks, zb = blockIdx.y % rt.head_blocks, r = blockIdx.z;
     const int group = a.H / a.Hkv;
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const TileRows tr = tile_rows(rt, blockIdx.x, group);
     const int first_head = zb * kMmaHeads;
-    const int n_rows = tr.gp == kMmaHeads ? min(kMmaHeads, group - first_head) : tr.ntok * tr.gp;
-    const size_t stride = static_cast<size_t>(kMmaHeads) * (a.vd + 2);
-    const float* ws = rt.workspace + (((static_cast<size_t>(blockIdx.x) * a.Hkv + g) * rt.head_blocks + zb) * rt.splits) * stride;
-    for (int r = warp; r < n_rows; r += 4) {
-        const int head = g * group + first_head + tr.head(r);
-        const float* row = ws + static_cast<size_t>(r) * (a.vd + 2);
-        float M = a.sinks ? a.sinks[head] : -INFINITY;
-        for (int s = 0; s < rt.splits; ++s) M = fmaxf(M, row[s * stride + a.vd]);
-        float L = a.sinks ? expf(a.sinks[head] - M) : 0.f;
-        for (int s = 0; s < rt.splits; ++s) {
-            const float ms = row[s * stride + a.vd];
-            if (ms != -INFINITY) L += row[s * stride + a.vd + 1] * expf(ms - M);
-        }
-        const size_t ob = static_cast<size_t>(tr.row0 + tr.token(r)) * a.ldo + static_cast<size_t>(head) * a.vd;
-        for (int d = lane; d < a.vd; d += 32) {
-            float v = 0.f;
-            for (int s = 0; s < rt.splits; ++s) {
-                const float ms = row[s * stride + a.vd];
-                if (ms != -INFINITY) v += row[s * stride + d] * expf(ms - M);
-            }
-            v /= L;
-            if (a.out_is_f32) static_cast<float*>(a.out)[ob + d] = v;
-            else static_cast<__nv_bfloat16*>(a.out)[ob + d] = __float2bfloat16_rn(v);
-        }
+    const int n_rows = (rt.block_rows == kMmaHeads && tr.gp == kMmaHeads) ? min(kMmaHeads, group - first_head) : tr.ntok * tr.gp;
+    if (r >= n_rows) return;
+    const size_t stride = static_cast<size_t>(rt.block_rows) * (a.vd + 2);
+    const float* row = rt.workspace + (((static_cast<size_t>(blockIdx.x) * a.Hkv + g) * rt.head_blocks + zb) * rt.splits) * stride +
+                       static_cast<size_t>(r) * (a.vd + 2);
+    const int head = g * group + first_head + tr.head(r);
+    if (threadIdx.x < 32) {
+        const int s = threadIdx.x;
+        const float ms = s < rt.splits ? row[s * stride + a.vd] : -INFINITY;
+        const float ls = s < rt.splits ? row[s * stride + a.vd + 1] : 0.f;
+        float M = warp_max(ms);
+        if (a.sinks) M = fmaxf(M, a.sinks[head]);
+        const float w = ms == -INFINITY ? 0.f : expf(ms - M);
+        float L = 0.f;
+        for (int i = 0; i < rt.splits; ++i) L += __shfl_sync(0xffffffffu, ls * w, i);       // in the ranges' order
+        if (a.sinks) L += expf(a.sinks[head] - M);
+        if (s < 16) s_w[s] = w;
+        if (s == 0) s_inv = 1.0f / L;
+    }
+    __syncthreads();
+    const size_t ob = static_cast<size_t>(tr.row0 + tr.token(r)) * a.ldo + static_cast<size_t>(head) * a.vd;
+    for (int d = threadIdx.x; d < a.vd; d += 128) {
+        float v = 0.f;
+#pragma unroll 4
+        for (int s = 0; s < rt.splits; ++s) v = fmaf(row[s * stride + d], s_w[s], v);
+        v *= s_inv;
+        if (a.out_is_f32) static_cast<float*>(a.out)[ob + d] = v;
+        else static_cast<__nv_bfloat16*>(a.out)[ob + d] = __float2bfloat16_rn(v);
     }
 }
 
-template <int NV>
+template <int NV, bool OWN>
 static int launch_rows_mma(const RowsArgs& a, const RowTiles& rt, int n_tiles, size_t smem, cudaStream_t st) {
-    auto kernel = attention_rows_mma_kernel<NV>;
+    auto kernel = attention_rows_mma_kernel<NV, OWN>;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
         if (e != cudaSuccess) { set_error("attention_rows: %s", cudaGetErrorString(e)); return 1; }
@@ -508,7 +559,7 @@ static int launch_rows_mma(const RowsArgs& a, const RowTiles& rt, int n_tiles, s
     launch_kernel(kernel, dim3(n_tiles, a.Hkv, rt.head_blocks * rt.splits), dim3(128), smem, st, a, rt);
     if (check_launch("attention_rows (tensor cores)")) return 1;
     if (rt.splits > 1) {
-        launch_kernel(attention_rows_merge_kernel, dim3(n_tiles, a.Hkv, rt.head_blocks), dim3(128), 0, st, a, rt);
+        launch_kernel(attention_rows_merge_kernel, dim3(n_tiles, a.Hkv * rt.head_blocks, rt.block_rows), dim3(128), 0, st, a, rt);
         return check_launch("attention_rows (merge)");
     }
     return 0;
@@ -547,10 +598,14 @@ extern "C" int gi_attention_rows_supported(int hd, int vd) {
     return hd >= 1 && hd <= kRowsMaxHeadDim && vd >= 1 && vd <= kRowsMaxValueDim;
 }
 
-static size_t rows_mma_smem(int hd, int vd, bool alias) {
+// Whether every warp owns sixteen rows of a block of 64 (small heads) instead of the four warps sharing sixteen.
+static bool rows_mma_own(int group, int hd, int vd) { return hd <= 128 && vd <= 128 && group <= kMmaHeads; }
+
+static size_t rows_mma_smem(int group, int hd, int vd, bool alias) {
     const int qs = hd + kMmaPad, vs = vd + kMmaPad;
-    return static_cast<size_t>(kMmaHeads + 2 * kRowsTile) * qs * 2 + (alias ? 0 : static_cast<size_t>(2 * kRowsTile) * vs * 2) +
-           static_cast<size_t>(4 * kMmaHeads * kMmaSStride) * 4;
+    const bool own = rows_mma_own(group, hd, vd);
+    return static_cast<size_t>((own ? kMmaOwnRows : kMmaHeads) + 2 * kRowsTile) * qs * 2 + (alias ? 0 : static_cast<size_t>(2 * kRowsTile) * vs * 2) +
+           (own ? 0 : static_cast<size_t>(4 * kMmaHeads * kMmaSStride) * 4);
 }
 
 // How many consecutive tokens of one request share a tile of the tensor-core form (16 / group, at least 1), or 0 when
@@ -558,8 +613,9 @@ static size_t rows_mma_smem(int hd, int vd, bool alias) {
 // in whole 64s up to 512.
 extern "C" int gi_attention_rows_tile_tokens(int H, int Hkv, int hd, int vd, int values_in_keys) {
     if (!g_rows_mma || Hkv <= 0 || H % Hkv || hd % 16 || vd % 64 || vd > kRowsMaxValueDim || hd > kRowsMaxHeadDim) return 0;
-    if (rows_mma_smem(hd, vd, values_in_keys != 0) > 200 * 1024) return 0;
     const int group = H / Hkv;
+    if (rows_mma_smem(group, hd, vd, values_in_keys != 0) > 200 * 1024) return 0;
+    if (rows_mma_own(group, hd, vd)) return kMmaOwnRows / group;
     return group >= kMmaHeads ? 1 : kMmaHeads / group;
 }
 
@@ -597,16 +653,20 @@ static int gi_attention_rows_impl(const void* q, int q_dtype, int ldq, const voi
         rt.list = tile_list; rt.kind = list_kind;
         rt.head_blocks = (group + kMmaHeads - 1) / kMmaHeads;
         rt.splits = splits > 1 ? splits : 1;
+        const bool own = rows_mma_own(group, hd, vd);
+        rt.block_rows = own ? kMmaOwnRows : kMmaHeads;
         rt.workspace = workspace;
         const int tiles = list_kind == 0 ? T : n_tiles;
         GI_REQUIRE(list_kind == 0 || tile_list != nullptr, "attention_rows: the list of tiles is missing");
-        GI_REQUIRE(rt.splits == 1 || (workspace != nullptr && static_cast<long long>(tiles) * Hkv * rt.head_blocks * rt.splits * kMmaHeads * (vd + 2) <= workspace_floats),
+        GI_REQUIRE(rt.splits == 1 || (workspace != nullptr && static_cast<long long>(tiles) * Hkv * rt.head_blocks * rt.splits * rt.block_rows * (vd + 2) <= workspace_floats),
                    "attention_rows: the workspace of the key ranges is missing or too small");
-        GI_REQUIRE(rt.head_blocks * rt.splits <= 65535, "attention_rows: too many blocks of heads and ranges of keys");
-        const size_t smem_mma = rows_mma_smem(hd, vd, a.alias != 0);
-        if (vd <= 128) return launch_rows_mma<4>(a, rt, tiles, smem_mma, st);
-        if (vd <= 256) return launch_rows_mma<8>(a, rt, tiles, smem_mma, st);
-        return launch_rows_mma<16>(a, rt, tiles, smem_mma, st);
+        GI_REQUIRE(rt.head_blocks * rt.splits <= 65535 && a.Hkv * rt.head_blocks <= 65535 && rt.splits <= 16,
+                   "attention_rows: too many blocks of heads or ranges of keys (at most 16 ranges)");
+        const size_t smem_mma = rows_mma_smem(group, hd, vd, a.alias != 0);
+        if (own) return vd <= 64 ? launch_rows_mma<8, true>(a, rt, tiles, smem_mma, st) : launch_rows_mma<16, true>(a, rt, tiles, smem_mma, st);
+        if (vd <= 128) return launch_rows_mma<4, false>(a, rt, tiles, smem_mma, st);
+        if (vd <= 256) return launch_rows_mma<8, false>(a, rt, tiles, smem_mma, st);
+        return launch_rows_mma<16, false>(a, rt, tiles, smem_mma, st);
     }
     // rows of the key tile: pairs of values are read by 32 lanes from 32 rows, free of bank conflicts when the row
     // length counted in pairs is odd

@@ -312,7 +312,8 @@ def attention_rows_tensor_cores(on: Optional[bool] = None) -> bool:
 
 def attention_rows_tile_tokens(num_heads: int, num_kv_heads: int, head_dim: int, value_dim: int, values_in_keys: bool) -> int:
     """How many consecutive tokens of one request share a tile of the tensor-core form of ``attention_rows`` over a
-    bfloat16 cache (16 // heads per key/value head, at least 1); 0 when that form does not serve these sizes."""
+    bfloat16 cache (64 // heads per key/value head for head and value sizes up to 128, where every warp owns sixteen
+    rows; else 16 // heads per key/value head, at least 1); 0 when that form does not serve these sizes."""
     return int(lib().gi_attention_rows_tile_tokens(num_heads, num_kv_heads, head_dim, value_dim, int(values_in_keys)))
 
 
@@ -330,7 +331,7 @@ def attention_rows_splits(n_tiles: int, num_heads: int, num_kv_heads: int, span:
 
 def attention_rows_workspace_rows(n_tiles: int, num_heads: int, num_kv_heads: int, splits: int) -> int:
     """Rows [value_dim + 2] of 32-bit workspace that a launch cut into ``splits`` ranges of keys needs."""
-    return n_tiles * num_kv_heads * ((num_heads // num_kv_heads + 15) // 16) * splits * 16 if splits > 1 else 0
+    return n_tiles * num_kv_heads * ((num_heads // num_kv_heads + 15) // 16) * splits * 64 if splits > 1 else 0      # up to 64 rows a tile
 
 
 def attention_rows(q: torch.Tensor, k_cache: torch.Tensor, v_cache: Optional[torch.Tensor], out: torch.Tensor,
@@ -398,7 +399,7 @@ def attention_rows_of_step(ctx, q: torch.Tensor, k_cache: torch.Tensor, v_cache:
         ws = None
         if splits > 1:
             ws = ctx.scratch("attention_rows_ranges_" + name, (attention_rows_workspace_rows(n, num_heads, num_kv_heads, splits), value_dim + 2),
-                             torch.float32, capacity=(_ROWS_BLOCKS + 16) * 16)
+                             torch.float32, capacity=(_ROWS_BLOCKS + 16) * 64)
         attention_rows(q, k_cache, v_cache, out, ctx.row_req, ctx.positions, tables, num_heads, num_kv_heads, head_dim, value_dim,
                        ctx.page_size, scale, splits=splits, workspace=ws, **{name: lst}, **common)
 
