@@ -290,12 +290,14 @@ attention_rows_mma_kernel(const RowsArgs a, const RowTiles rt) {
     const int per_split = (all_tiles + rt.splits - 1) / rt.splits;
     const int it0 = split * per_split, it1 = min(all_tiles, it0 + per_split);
 
-    auto fetch = [&](int tile, int stage) {
-        const int base = lo_t + tile * kRowsTile;
-        // lane j looks up the page row of key j: one load in flight per lane instead of a chain of dependent ones
-        const int pl = base + lane;
-        long long my_row = -1;
-        if (pl <= hi_t) my_row = (static_cast<long long>(table[pl / a.page_size]) * a.Hkv + g) * a.page_size + (pl % a.page_size);
+    // lane j looks up the page row of key j of a tile: one load in flight per lane instead of a chain of dependent ones;
+    // the rows of the tile after the next are asked for before the current tile's products, a tile ahead of their use
+    auto lookup = [&](int tile) -> long long {
+        const int pl = lo_t + tile * kRowsTile + lane;
+        if (tile >= it1 || pl > hi_t) return -1;
+        return (static_cast<long long>(table[pl / a.page_size]) * a.Hkv + g) * a.page_size + (pl % a.page_size);
+    };
+    auto fetch = [&](long long my_row, int stage) {
         for (int j = warp; j < kRowsTile; j += 4) {
             const long long rj = __shfl_sync(0xffffffffu, my_row, j);
             const bool in = rj >= 0;
@@ -312,7 +314,8 @@ attention_rows_mma_kernel(const RowsArgs a, const RowTiles rt) {
         rows_cp_async_commit();
     };
 
-    if (it0 < it1) fetch(it0, 0);
+    if (it0 < it1) fetch(lookup(it0), 0);
+    long long next_rows = lookup(it0 + 1);
     // the queries, a warp per row: 16-byte loads where the rows allow them
     for (int r = warp; r < RT; r += 4) {
         bf* dst = s_q + r * qs;
@@ -365,7 +368,8 @@ attention_rows_mma_kernel(const RowsArgs a, const RowTiles rt) {
         const int st = (it - it0) & 1;
         rows_cp_async_wait_all();
         __syncthreads();                                 // tile ``it`` is there; everyone is done with the other stage
-        if (it + 1 < it1) fetch(it + 1, st ^ 1);
+        if (it + 1 < it1) fetch(next_rows, st ^ 1);
+        next_rows = lookup(it + 2);
         const bf* kt = s_k + st * kRowsTile * qs;
         const bf* vt = s_v + st * kRowsTile * vs;
         // S = Q K^T, this warp's slices of the head dimension

@@ -146,7 +146,7 @@ grouped_product_kernel(const GroupedArgs p) {
 // over more than a hundred blocks per tile. An output element is the sum of its lanes' partial sums (lane l takes the
 // pieces l, l + 32, ...), added by a fixed xor tree: it depends on its own row only.
 constexpr int kGrRows = 32;           // output rows per block
-constexpr int kGrFew = 4;             // up to this many rows in a tile the warp's four weight rows are streamed together
+constexpr int kGrFew = 4;             // rows of a tile that are multiplied with a piece of the weights while it is in registers
 
 template <typename T> struct Vec16;
 template <> struct Vec16<float> {
@@ -197,14 +197,16 @@ grouped_rows_kernel(const GroupedArgs p) {
     const TA* A = static_cast<const TA*>(p.a) + p.a_off + static_cast<size_t>(g) * p.a_gs;
     const TW* W = static_cast<const TW*>(p.w) + static_cast<size_t>(g) * p.w_gs;
     const int pieces = p.K / PIECE;
-    if (m_count <= kGrFew) {
-        // few rows in the tile (the usual case when decoding): the warp's four weight rows are streamed together, eight
-        // 16-byte loads of a lane in flight, and every input piece is read once for the four
-        const int n_first = blockIdx.y * kGrRows + warp * 4;
-        if (n_first >= p.N) return;
-        const TW* wrow[4];
+    // The warp's four weight rows are streamed together, eight 16-byte loads of a lane in flight, and every input piece is
+    // read once for the four. The tile's rows are taken four at a time (a tile of a decode step seldom has more); a
+    // second group of four streams the same weight rows again, from the L2 cache.
+    const int n_first = blockIdx.y * kGrRows + warp * 4;
+    if (n_first >= p.N) return;
+    const TW* wrow[4];
 #pragma unroll
-        for (int r = 0; r < 4; ++r) wrow[r] = W + static_cast<size_t>(min(n_first + r, p.N - 1)) * p.ldw;
+    for (int r = 0; r < 4; ++r) wrow[r] = W + static_cast<size_t>(min(n_first + r, p.N - 1)) * p.ldw;
+    for (int m0 = 0; m0 < m_count; m0 += kGrFew) {
+        const int m_here = min(kGrFew, m_count - m0);
         float acc[4][kGrFew], acc_up[GATED ? 4 : 1][kGrFew];
 #pragma unroll
         for (int r = 0; r < 4; ++r) {
@@ -220,10 +222,10 @@ grouped_rows_kernel(const GroupedArgs p) {
             }
 #pragma unroll
             for (int i = 0; i < kGrFew; ++i) {
-                if (i < m_count) {
-                    const TA* arow = A + static_cast<size_t>(s_row[i] / p.a_div) * p.lda + c * PIECE;
+                if (i < m_here) {
+                    const TA* arow = A + static_cast<size_t>(s_row[m0 + i] / p.a_div) * p.lda + c * PIECE;
                     float av[8];
-                    if (sizeof(TA) == 4 && PIECE == 8) {
+                    if (sizeof(TA) == 4 && PIECE == 8) {          // 32-bit inputs against bfloat16 weights: two loads
                         float lo4[8], hi4[8];
                         Vec16<float>::load(reinterpret_cast<const float*>(arow), lo4);
                         Vec16<float>::load(reinterpret_cast<const float*>(arow) + 4, hi4);
@@ -247,61 +249,14 @@ grouped_rows_kernel(const GroupedArgs p) {
         for (int r = 0; r < 4; ++r) {
 #pragma unroll
             for (int i = 0; i < kGrFew; ++i) {
-                if (i < m_count && n_first + r < p.N) {
+                if (i < m_here && n_first + r < p.N) {
                     float v = warp_sum(acc[r][i]);
                     if (GATED) v = gp_act(v, p.act) * warp_sum(acc_up[GATED ? r : 0][i]);
                     if (lane == 0) {
-                        const size_t o = static_cast<size_t>(s_row[i]) * p.ldo + p.o_off + static_cast<size_t>(g) * p.o_gs + n_first + r;
+                        const size_t o = static_cast<size_t>(s_row[m0 + i]) * p.ldo + p.o_off + static_cast<size_t>(g) * p.o_gs + n_first + r;
                         if (p.out_is_f32) static_cast<float*>(p.out)[o] = v;
                         else static_cast<__nv_bfloat16*>(p.out)[o] = __float2bfloat16_rn(v);
                     }
-                }
-            }
-        }
-        return;
-    }
-    for (int rr = 0; rr < kGrRows / 8; ++rr) {
-        const int n = blockIdx.y * kGrRows + rr * 8 + warp;
-        if (n >= p.N) break;
-        const TW* wrow = W + static_cast<size_t>(n) * p.ldw;
-        float acc[kGpTM], acc_up[GATED ? kGpTM : 1];
-#pragma unroll
-        for (int i = 0; i < kGpTM; ++i) { acc[i] = 0.f; if (GATED) acc_up[GATED ? i : 0] = 0.f; }
-        for (int c = lane; c < pieces; c += 32) {
-            float wv[8], uv[8];
-            Vec16<TW>::load(wrow + c * PIECE, wv);
-            if (GATED) Vec16<TW>::load(wrow + p.up_off + c * PIECE, uv);
-#pragma unroll
-            for (int i = 0; i < kGpTM; ++i) {
-                if (i < m_count) {
-                    const TA* arow = A + static_cast<size_t>(s_row[i] / p.a_div) * p.lda + c * PIECE;
-                    float av[8];
-                    if (sizeof(TA) == 4 && PIECE == 8) {          // 32-bit inputs against bfloat16 weights: two loads
-                        float lo4[8], hi4[8];
-                        Vec16<float>::load(reinterpret_cast<const float*>(arow), lo4);
-                        Vec16<float>::load(reinterpret_cast<const float*>(arow) + 4, hi4);
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) { av[j] = lo4[j]; av[4 + j] = hi4[j]; }
-                    } else {
-                        Vec16<TA>::load(arow, av);
-                    }
-#pragma unroll
-                    for (int j = 0; j < PIECE; ++j) {
-                        acc[i] = fmaf(av[j], wv[j], acc[i]);
-                        if (GATED) acc_up[GATED ? i : 0] = fmaf(av[j], uv[j], acc_up[GATED ? i : 0]);
-                    }
-                }
-            }
-        }
-#pragma unroll
-        for (int i = 0; i < kGpTM; ++i) {
-            if (i < m_count) {
-                float v = warp_sum(acc[i]);
-                if (GATED) v = gp_act(v, p.act) * warp_sum(acc_up[GATED ? i : 0]);
-                if (lane == 0) {
-                    const size_t o = static_cast<size_t>(s_row[i]) * p.ldo + p.o_off + static_cast<size_t>(g) * p.o_gs + n;
-                    if (p.out_is_f32) static_cast<float*>(p.out)[o] = v;
-                    else static_cast<__nv_bfloat16*>(p.out)[o] = __float2bfloat16_rn(v);
                 }
             }
         }
