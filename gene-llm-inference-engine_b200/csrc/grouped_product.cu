@@ -263,6 +263,88 @@ grouped_rows_kernel(const GroupedArgs p) {
     }
 }
 
+// The heads form for many rows (prompt portions): tiles of 64 rows x 64 outputs, a thread 4 x 4 of them, so that two
+// 16-byte reads of shared memory feed sixteen multiply-adds. Inputs 32-bit or bfloat16, weights likewise; rows of four
+// values must be aligned (the caller checks). An output element is one chain of multiply-adds in the order of k.
+constexpr int kG64 = 64, kG64K = 16;
+
+template <typename T> __device__ __forceinline__ float4 load4(const T* p);
+template <> __device__ __forceinline__ float4 load4<float>(const float* p) { return *reinterpret_cast<const float4*>(p); }
+template <> __device__ __forceinline__ float4 load4<__nv_bfloat16>(const __nv_bfloat16* p) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(p);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+    return make_float4(a.x, a.y, b.x, b.y);
+}
+
+template <typename TA, typename TW>
+__global__ void __launch_bounds__(256)
+head_product64_kernel(const GroupedArgs p) {
+    pdl_prologue();
+    __shared__ __align__(16) float s_a[kG64K][kG64 + 4];
+    __shared__ __align__(16) float s_w[kG64K][kG64 + 4];
+    const int tid = threadIdx.x;
+    const int g = blockIdx.x % p.groups;
+    const int row0 = (blockIdx.x / p.groups) * kG64;
+    const int n0 = blockIdx.y * kG64;
+    const TA* A = static_cast<const TA*>(p.a) + p.a_off + static_cast<size_t>(g) * p.a_gs;
+    const TW* W = static_cast<const TW*>(p.w) + static_cast<size_t>(g) * p.w_gs;
+
+    if (p.tail > 0 && blockIdx.y == 0) {            // the rotated tail, by the blocks of the first tile of outputs
+        for (int i = tid; i < kG64 * (p.tail / 2); i += 256) {
+            const int m = i / (p.tail / 2), pr = i % (p.tail / 2);
+            const int r = row0 + m;
+            if (r >= p.rows) continue;
+            const TA* src = A + static_cast<size_t>(r) * p.lda + p.K + 2 * pr;
+            float sn, cs;
+            sincosf(static_cast<float>(p.positions[r]) * p.freq[pr], &sn, &cs);
+            sn *= p.amplitude; cs *= p.amplitude;
+            const float u = to_float(src[0]), v = to_float(src[1]);
+            const size_t o = static_cast<size_t>(r) * p.ldo + p.o_off + static_cast<size_t>(g) * p.o_gs + p.N + 2 * pr;
+            const float ru = u * cs - v * sn, rv = v * cs + u * sn;
+            if (p.out_is_f32) { static_cast<float*>(p.out)[o] = ru; static_cast<float*>(p.out)[o + 1] = rv; }
+            else { static_cast<__nv_bfloat16*>(p.out)[o] = __float2bfloat16_rn(ru); static_cast<__nv_bfloat16*>(p.out)[o + 1] = __float2bfloat16_rn(rv); }
+        }
+    }
+
+    const int lr = tid >> 2, lk = (tid & 3) * 4;             // what this thread brings in: row (or output) lr, values lk..lk+3
+    const int ty = (tid >> 4) * 4, tx = (tid & 15) * 4;      // its 4 x 4 outputs
+    float acc[4][4] = {};
+    for (int k0 = 0; k0 < p.K; k0 += kG64K) {
+        float4 av = make_float4(0.f, 0.f, 0.f, 0.f), wv = av;
+        if (row0 + lr < p.rows && k0 + lk < p.K) av = load4<TA>(A + static_cast<size_t>(row0 + lr) * p.lda + k0 + lk);
+        if (n0 + lr < p.N && k0 + lk < p.K) wv = load4<TW>(W + static_cast<size_t>(n0 + lr) * p.ldw + k0 + lk);
+        __syncthreads();                                      // the tile before is done with
+        s_a[lk][lr] = av.x; s_a[lk + 1][lr] = av.y; s_a[lk + 2][lr] = av.z; s_a[lk + 3][lr] = av.w;
+        s_w[lk][lr] = wv.x; s_w[lk + 1][lr] = wv.y; s_w[lk + 2][lr] = wv.z; s_w[lk + 3][lr] = wv.w;
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < kG64K; ++k) {
+            const float4 a4 = *reinterpret_cast<const float4*>(&s_a[k][ty]);
+            const float4 w4 = *reinterpret_cast<const float4*>(&s_w[k][tx]);
+            const float ar[4] = {a4.x, a4.y, a4.z, a4.w}, wr[4] = {w4.x, w4.y, w4.z, w4.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(ar[i], wr[j], acc[i][j]);
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int r = row0 + ty + i;
+        if (r >= p.rows) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int n = n0 + tx + j;
+            if (n >= p.N) continue;
+            const size_t o = static_cast<size_t>(r) * p.ldo + p.o_off + static_cast<size_t>(g) * p.o_gs + n;
+            if (p.out_is_f32) static_cast<float*>(p.out)[o] = acc[i][j];
+            else static_cast<__nv_bfloat16*>(p.out)[o] = __float2bfloat16_rn(acc[i][j]);
+        }
+    }
+}
+
 // ------------------------------------------------------------------------------------------------ routing
 constexpr int kRouteMaxExperts = 1024;
 
@@ -433,6 +515,18 @@ static int gi_head_product_impl(const void* a, int a_dtype, long long lda, int a
     const long long tiles = static_cast<long long>((rows + kGpTM - 1) / kGpTM) * heads;
     GI_REQUIRE(tiles <= 2147483647LL, "head_product: too many tiles");
     dim3 grid(static_cast<unsigned>(tiles), (N + kGpTN - 1) / kGpTN);
+    // many tokens: tiles of 64 x 64 where every group of four values is aligned (K in whole fours: no ragged piece)
+    if (rows >= 2 * kG64 && K % 4 == 0 && lda % 4 == 0 && a_off % 4 == 0 && a_gs % 4 == 0 && w_gs % 4 == 0 &&
+        reinterpret_cast<uintptr_t>(a) % 16 == 0 && reinterpret_cast<uintptr_t>(w) % 16 == 0 && !(a_dtype == kBF16 && w_dtype == kF32)) {
+        const long long tiles64 = static_cast<long long>((rows + kG64 - 1) / kG64) * heads;
+        GI_REQUIRE(tiles64 <= 2147483647LL, "head_product: too many tiles");
+        dim3 grid64(static_cast<unsigned>(tiles64), (N + kG64 - 1) / kG64);
+        cudaStream_t st64 = static_cast<cudaStream_t>(stream);
+        if (a_dtype == kF32 && w_dtype == kF32) launch_kernel((head_product64_kernel<float, float>), grid64, dim3(256), 0, st64, p);
+        else if (a_dtype == kF32) launch_kernel((head_product64_kernel<float, __nv_bfloat16>), grid64, dim3(256), 0, st64, p);
+        else launch_kernel((head_product64_kernel<__nv_bfloat16, __nv_bfloat16>), grid64, dim3(256), 0, st64, p);
+        return check_launch("head_product (tiles of 64)");
+    }
     // few tokens: the heads' matrices are what is read; the rotated tail stays with the tiled form
     if (rows <= 2 * kGpTM && tail == 0 && rows_form_fits(p, a_dtype, w_dtype))
         return launch_grouped_rows<false>(p, a_dtype, w_dtype, static_cast<unsigned>(tiles), static_cast<cudaStream_t>(stream));

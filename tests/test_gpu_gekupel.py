@@ -203,8 +203,9 @@ def test_attention_rows_in_tiles_and_ranges_of_keys(H, Hkv, hd, vd, window, chun
 def test_head_product_with_a_rotated_tail(dtype):
     from geneinfer_b200.ops import kernels
     g = torch.Generator().manual_seed(4)
-    for T, H, N, K, tail, off in ((37, 3, 70, 24, 8, 5), (1, 5, 8, 100, 0, 5), (16, 2, 64, 32, 2, 5), (3, 4, 40, 64, 0, 8), (20, 2, 33, 48, 0, 16)):
-        a = torch.randn(T, off + H * (K + tail) + 3, generator=g)
+    for T, H, N, K, tail, off in ((37, 3, 70, 24, 8, 5), (1, 5, 8, 100, 0, 5), (16, 2, 64, 32, 2, 5), (3, 4, 40, 64, 0, 8), (20, 2, 33, 48, 0, 16),
+                                  (200, 3, 70, 24, 8, 8), (129, 2, 64, 100, 0, 4), (300, 1, 130, 36, 4, 0)):
+        a = torch.randn(T, off + H * (K + tail) + (4 if off % 4 == 0 else 3), generator=g)
         w = _bf(torch.randn(H, N, K, generator=g))
         freq = torch.rand(max(tail // 2, 1), generator=g)[:tail // 2]
         pos = torch.randint(0, 900, (T,), generator=g)
@@ -438,6 +439,69 @@ def test_attention_block_edge_and_sink(qi, ki, decoded):
     if qi // 11 != ki // 11:
         no_sink = dict(_dbl(w), sink=torch.full((6,), -30.0, dtype=F))
         assert float((pg.attention_mixer(x.double(), ATT, no_sink, 1e-5, torch.arange(T))[qi] - want[qi]).abs().max()) > 0.02
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("decoded", [False, True])
+@pytest.mark.parametrize("distance", [299, 300])
+def test_latent_far_key_among_hundreds(distance, decoded, dtype):
+    """A window of 300 over 330 tokens: one key 299 back decides the output, the same key 300 back is not seen; in
+    bfloat16 the tensor-core kernel walks ten key tiles for it, as a prompt portion and token by token."""
+    far = dict(LAT, mask={"size": 300})
+    D, T, qi = 56, 330, 325
+    g = torch.Generator().manual_seed(14)
+    w = _lat_weights(D, far, g, True, std=0.1)
+    for name in ("dq", "dkv"):
+        w[name][:, :2] = 0
+    w["dkv"][0, 0] = 3.0
+    w["dq"][0, 1] = 3.0
+    w["uq"][:] = 0
+    w["uk"][:] = 0
+    for h in range(far["heads"]):
+        w["uq"][h * 32, 0] = 4.0
+        w["uk"][h * 24, 0] = 4.0
+    part = _lat_part(D, far, w, dtype, True)
+    x = 0.3 * torch.randn(T, D, generator=g)
+    x[:, :2] = 0
+    x[qi - distance, 0] = 6.0
+    x[qi, 1] = 6.0
+    x = _bf(x)
+    cuts = [[T]] if not decoded else [[qi - 2]] + [[1]] * (T - qi + 2)
+    got = _run_mixer(part, PagesCtx(dtype, 1, 1, 56, 0, max_len=512), [x], cuts, dtype, D)[0]
+    want = pg.latent_attention_mixer(x.double(), far, _dbl(w), 1e-5, torch.arange(T), True)
+    _close(got, want, dtype, f"key {distance} back", b16=3e-2)
+    x2 = x.clone()
+    x2[qi - distance, 0] = 0
+    moved = float((pg.latent_attention_mixer(x2.double(), far, _dbl(w), 1e-5, torch.arange(T), True)[qi] - want[qi]).abs().max())
+    assert (moved > 0.1) == (distance < 300), f"the key {distance} back moves the output by {moved}"
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("decoded", [False, True])
+def test_attention_far_key_inside_a_long_block(decoded, dtype):
+    """Blocks of 500 positions: the key 400 back lies in the query's block and is seen by the heads whose bias is small."""
+    far = dict(ATT, mask={"size": 500})
+    D, T, qi, ki = 48, 440, 430, 30
+    g = torch.Generator().manual_seed(15)
+    w = _att_weights(D, far, g, std=0.1)
+    w["q"][:, :2] = 0
+    w["k"][:, :2] = 0
+    w["q"][::16, 1] = 5.0
+    w["k"][::16, 0] = 5.0
+    part = _att_part(D, far, w, dtype)
+    x = 0.3 * torch.randn(T, D, generator=g)
+    x[:, :2] = 0
+    x[ki, 0] = 6.0
+    x[qi, 1] = 6.0
+    x = _bf(x)
+    cuts = [[T]] if not decoded else [[qi - 2]] + [[1]] * (T - qi + 2)
+    got = _run_mixer(part, PagesCtx(dtype, 1, 2, 16, 24, max_len=512), [x], cuts, dtype, D)[0]
+    want = pg.attention_mixer(x.double(), far, _dbl(w), 1e-5, torch.arange(T))
+    _close(got, want, dtype, "far key in the block", b16=3e-2)
+    x2 = x.clone()
+    x2[ki, 0] = 0
+    moved = float((pg.attention_mixer(x2.double(), far, _dbl(w), 1e-5, torch.arange(T))[qi] - want[qi]).abs().max())
+    assert moved > 0.05, f"the far key moves the output by {moved} only"
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
