@@ -255,13 +255,18 @@ __device__ __forceinline__ int first_visible(const RowsArgs& a, int pos) {
     return lo;
 }
 
-// NV: 8-wide tiles of value dimensions per warp. OWN false: the four warps share sixteen rows (vd <= 32 NV); OWN true
-// (head and value sizes up to 128, groups of at most sixteen heads): every warp owns sixteen of the block's 64 rows,
-// with all of the head dimension and all value dimensions (vd <= 8 NV), so the warps exchange nothing.
-template <int NV, bool OWN>
+// NV: 8-wide tiles of value dimensions per warp. MODE 0: the four warps share sixteen rows, each with a quarter of the
+// head dimension of S and of the value dimensions (vd <= 32 NV). MODE 1 (head and value sizes up to 128, groups of at
+// most sixteen heads): every warp owns sixteen of the block's 64 rows, with all of the head dimension and all value
+// dimensions (vd <= 8 NV), so the warps exchange nothing. MODE 2 (sixteen or more heads to a key/value head, large
+// heads: the latent): two tokens of sixteen heads a block, two warps a token; each computes all of S for its token (the
+// price: S twice) and keeps half of the value dimensions (vd <= 16 NV), so again nothing is exchanged and two tokens
+// share every key tile.
+template <int NV, int MODE>
 __global__ void __launch_bounds__(128)
 attention_rows_mma_kernel(const RowsArgs a, const RowTiles rt) {
-    constexpr int RT = OWN ? kMmaOwnRows : kMmaHeads;
+    constexpr bool OWN = MODE == 1, PAIR = MODE == 2;
+    constexpr int RT = OWN ? kMmaOwnRows : PAIR ? 2 * kMmaHeads : kMmaHeads;
     pdl_prologue();
     extern __shared__ __align__(16) unsigned char smem_raw[];
     using bf = __nv_bfloat16;
@@ -273,6 +278,7 @@ attention_rows_mma_kernel(const RowsArgs a, const RowTiles rt) {
     const int first_head = zb * kMmaHeads;
     const int n_heads = min(kMmaHeads, group - first_head);
     const int n_rows = (!OWN && tr.gp == kMmaHeads) ? n_heads : tr.ntok * tr.gp;
+    auto row_on = [&](int r) { return PAIR ? ((r >> 4) < tr.ntok && (r & 15) < n_heads) : r < n_rows; };
     const int qs = a.hd + kMmaPad;                     // row length of the query and key tiles
     const int vs = a.alias ? qs : a.vd + kMmaPad;
     bf* s_q = reinterpret_cast<bf*>(smem_raw);                              // [16][qs]
@@ -319,7 +325,7 @@ attention_rows_mma_kernel(const RowsArgs a, const RowTiles rt) {
     // the queries, a warp per row: 16-byte loads where the rows allow them
     for (int r = warp; r < RT; r += 4) {
         bf* dst = s_q + r * qs;
-        if (r >= n_rows) {
+        if (!row_on(r)) {
             for (int d = lane; d < a.hd; d += 32) dst[d] = __float2bfloat16_rn(0.f);
             continue;
         }
@@ -345,7 +351,7 @@ attention_rows_mma_kernel(const RowsArgs a, const RowTiles rt) {
     }
 
     const int gr = lane >> 2, tq = lane & 3;            // the fragment's rows gr and gr + 8 and its pair of columns
-    const int rb = OWN ? warp * kMmaHeads : 0;          // the first of this warp's sixteen rows
+    const int rb = OWN ? warp * kMmaHeads : PAIR ? (warp >> 1) * kMmaHeads : 0;      // the first of this warp's sixteen rows
     float o[NV][4];
 #pragma unroll
     for (int i = 0; i < NV; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
@@ -354,14 +360,14 @@ attention_rows_mma_kernel(const RowsArgs a, const RowTiles rt) {
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
         const int r = rb + gr + 8 * h;
-        const bool row_on = r < n_rows;
-        pos_r[h] = row_on ? pos0 + tr.token(r) : -1;              // a row that is not there sees no key
-        lo_r[h] = row_on ? first_visible(a, pos_r[h]) : 0;
-        if (a.slopes && row_on) slope[h] = a.slopes[g * group + first_head + tr.head(r)];
+        const bool on = row_on(r);
+        pos_r[h] = on ? pos0 + tr.token(r) : -1;                  // a row that is not there sees no key
+        lo_r[h] = on ? first_visible(a, pos_r[h]) : 0;
+        if (a.slopes && on) slope[h] = a.slopes[g * group + first_head + tr.head(r)];
     }
-    const int nv = OWN ? a.vd / 8 : a.vd / 32;           // 8-wide value tiles of this warp
-    const int v0 = OWN ? 0 : warp * (a.vd / 4);          // its first value dimension
-    const bool warp_on = !OWN || rb < n_rows;            // (a warp without rows only helps to fetch)
+    const int nv = OWN ? a.vd / 8 : PAIR ? a.vd / 16 : a.vd / 32;                     // 8-wide value tiles of this warp
+    const int v0 = OWN ? 0 : PAIR ? (warp & 1) * (a.vd / 2) : warp * (a.vd / 4);      // its first value dimension
+    const bool warp_on = OWN ? rb < n_rows : PAIR ? (warp >> 1) < tr.ntok : true;    // (a warp without rows only helps to fetch)
     const int k_steps = a.hd / 16;
 
     for (int it = it0; it < it1; ++it) {
@@ -379,7 +385,7 @@ attention_rows_mma_kernel(const RowsArgs a, const RowTiles rt) {
         const uint32_t q_addr = rows_smem_u32(s_q + (rb + (lane & 15)) * qs + (lane >> 4) * 8);
         const uint32_t k_addr = rows_smem_u32(kt + ((lane >> 4) * 8 + (lane & 7)) * qs + ((lane >> 3) & 1) * 8);
         if (warp_on) {
-            for (int ks = OWN ? 0 : warp; ks < k_steps; ks += OWN ? 1 : 4) {
+            for (int ks = MODE ? 0 : warp; ks < k_steps; ks += MODE ? 1 : 4) {
                 uint32_t qa[4];
                 rows_ldsm_x4(q_addr + ks * 32, qa[0], qa[1], qa[2], qa[3]);
 #pragma unroll
@@ -391,7 +397,7 @@ attention_rows_mma_kernel(const RowsArgs a, const RowTiles rt) {
                 }
             }
         }
-        if (!OWN) {
+        if (MODE == 0) {
             float* mine = s_s + warp * kMmaHeads * kMmaSStride;
 #pragma unroll
             for (int nt = 0; nt < 4; ++nt) {
@@ -406,7 +412,7 @@ attention_rows_mma_kernel(const RowsArgs a, const RowTiles rt) {
         float tile_max[2] = {-INFINITY, -INFINITY};
 #pragma unroll
         for (int nt = 0; nt < 4; ++nt) {
-            if (!OWN) {
+            if (MODE == 0) {
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
                     float2 sum2 = make_float2(0.f, 0.f);
@@ -483,14 +489,14 @@ attention_rows_mma_kernel(const RowsArgs a, const RowTiles rt) {
             for (int i = 0; i < NV; ++i) {
                 if (i < nv) { row[v0 + i * 8 + 2 * tq] = o[i][2 * h]; row[v0 + i * 8 + 2 * tq + 1] = o[i][2 * h + 1]; }
             }
-            if ((OWN || warp == 0) && tq == 0) { row[a.vd] = m[h]; row[a.vd + 1] = l[h]; }
+            if ((OWN || (PAIR && !(warp & 1)) || warp == 0) && tq == 0) { row[a.vd] = m[h]; row[a.vd + 1] = l[h]; }
         }
         return;
     }
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
         const int r = rb + gr + 8 * h;
-        if (r >= n_rows) continue;
+        if (!row_on(r)) continue;
         const int head = g * group + first_head + tr.head(r);
         float M = m[h], L = l[h], f = 1.f;
         if (a.sinks) {
@@ -522,8 +528,10 @@ attention_rows_merge_kernel(const RowsArgs a, const RowTiles rt) {
     const int group = a.H / a.Hkv;
     const TileRows tr = tile_rows(rt, blockIdx.x, group);
     const int first_head = zb * kMmaHeads;
-    const int n_rows = (rt.block_rows == kMmaHeads && tr.gp == kMmaHeads) ? min(kMmaHeads, group - first_head) : tr.ntok * tr.gp;
-    if (r >= n_rows) return;
+    const int n_heads = min(kMmaHeads, group - first_head);
+    const bool on = rt.block_rows == 2 * kMmaHeads ? ((r >> 4) < tr.ntok && (r & 15) < n_heads)
+                  : (rt.block_rows == kMmaHeads && tr.gp == kMmaHeads) ? r < n_heads : r < tr.ntok * tr.gp;
+    if (!on) return;
     const size_t stride = static_cast<size_t>(rt.block_rows) * (a.vd + 2);
     const float* row = rt.workspace + (((static_cast<size_t>(blockIdx.x) * a.Hkv + g) * rt.head_blocks + zb) * rt.splits) * stride +
                        static_cast<size_t>(r) * (a.vd + 2);
@@ -553,9 +561,9 @@ attention_rows_merge_kernel(const RowsArgs a, const RowTiles rt) {
     }
 }
 
-template <int NV, bool OWN>
+template <int NV, int MODE>
 static int launch_rows_mma(const RowsArgs& a, const RowTiles& rt, int n_tiles, size_t smem, cudaStream_t st) {
-    auto kernel = attention_rows_mma_kernel<NV, OWN>;
+    auto kernel = attention_rows_mma_kernel<NV, MODE>;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
         if (e != cudaSuccess) { set_error("attention_rows: %s", cudaGetErrorString(e)); return 1; }
@@ -595,6 +603,9 @@ static int launch_rows_vi(const RowsArgs& a, int T_rows, int blocks_z, int warps
 using namespace gi;
 
 static int g_rows_mma = 1;
+static int g_rows_pairs = 1;
+// 0: large heads run with the four warps sharing a token's sixteen rows instead of two tokens a block (for comparisons)
+extern "C" int gi_attention_rows_set_pairs(int on) { const int old = g_rows_pairs; g_rows_pairs = on ? 1 : 0; return old; }
 // 0: the CUDA-core form also where the tensor-core form applies (for comparisons); returns the old setting
 extern "C" int gi_attention_rows_set_mma(int on) { const int old = g_rows_mma; g_rows_mma = on ? 1 : 0; return old; }
 
@@ -605,12 +616,21 @@ extern "C" int gi_attention_rows_supported(int hd, int vd) {
 // Whether every warp owns sixteen rows of a block of 64 (small heads) instead of the four warps sharing sixteen.
 static bool rows_mma_own(int group, int hd, int vd) { return hd <= 128 && vd <= 128 && group <= kMmaHeads; }
 
-static size_t rows_mma_smem(int group, int hd, int vd, bool alias) {
+static size_t rows_mma_smem_of(int mode, int hd, int vd, bool alias) {
     const int qs = hd + kMmaPad, vs = vd + kMmaPad;
-    const bool own = rows_mma_own(group, hd, vd);
-    return static_cast<size_t>((own ? kMmaOwnRows : kMmaHeads) + 2 * kRowsTile) * qs * 2 + (alias ? 0 : static_cast<size_t>(2 * kRowsTile) * vs * 2) +
-           (own ? 0 : static_cast<size_t>(4 * kMmaHeads * kMmaSStride) * 4);
+    const int rows = mode == 1 ? kMmaOwnRows : mode == 2 ? 2 * kMmaHeads : kMmaHeads;
+    return static_cast<size_t>(rows + 2 * kRowsTile) * qs * 2 + (alias ? 0 : static_cast<size_t>(2 * kRowsTile) * vs * 2) +
+           (mode == 0 ? static_cast<size_t>(4 * kMmaHeads * kMmaSStride) * 4 : 0);
 }
+
+// 0: the warps share sixteen rows; 1: a warp owns sixteen of 64 rows; 2: two tokens of sixteen heads, two warps a token.
+static int rows_mma_mode(int group, int hd, int vd, bool alias) {
+    if (rows_mma_own(group, hd, vd)) return 1;
+    if (g_rows_pairs && group >= kMmaHeads && rows_mma_smem_of(2, hd, vd, alias) <= 113 * 1024) return 2;      // two blocks an SM
+    return 0;
+}
+
+static size_t rows_mma_smem(int group, int hd, int vd, bool alias) { return rows_mma_smem_of(rows_mma_mode(group, hd, vd, alias), hd, vd, alias); }
 
 // How many consecutive tokens of one request share a tile of the tensor-core form (16 / group, at least 1), or 0 when
 // that form does not serve these sizes (a bfloat16 cache is understood): the head size in whole 16s, the value size
@@ -619,7 +639,9 @@ extern "C" int gi_attention_rows_tile_tokens(int H, int Hkv, int hd, int vd, int
     if (!g_rows_mma || Hkv <= 0 || H % Hkv || hd % 16 || vd % 64 || vd > kRowsMaxValueDim || hd > kRowsMaxHeadDim) return 0;
     const int group = H / Hkv;
     if (rows_mma_smem(group, hd, vd, values_in_keys != 0) > 200 * 1024) return 0;
-    if (rows_mma_own(group, hd, vd)) return kMmaOwnRows / group;
+    const int mode = rows_mma_mode(group, hd, vd, values_in_keys != 0);
+    if (mode == 1) return kMmaOwnRows / group;
+    if (mode == 2) return 2;
     return group >= kMmaHeads ? 1 : kMmaHeads / group;
 }
 
@@ -657,8 +679,9 @@ static int gi_attention_rows_impl(const void* q, int q_dtype, int ldq, const voi
         rt.list = tile_list; rt.kind = list_kind;
         rt.head_blocks = (group + kMmaHeads - 1) / kMmaHeads;
         rt.splits = splits > 1 ? splits : 1;
-        const bool own = rows_mma_own(group, hd, vd);
-        rt.block_rows = own ? kMmaOwnRows : kMmaHeads;
+        int mode = rows_mma_mode(group, hd, vd, a.alias != 0);
+        if (mode == 2 && list_kind != 2) mode = 0;        // single tokens: all four warps on the one token
+        rt.block_rows = mode == 1 ? kMmaOwnRows : mode == 2 ? 2 * kMmaHeads : kMmaHeads;
         rt.workspace = workspace;
         const int tiles = list_kind == 0 ? T : n_tiles;
         GI_REQUIRE(list_kind == 0 || tile_list != nullptr, "attention_rows: the list of tiles is missing");
@@ -666,11 +689,12 @@ static int gi_attention_rows_impl(const void* q, int q_dtype, int ldq, const voi
                    "attention_rows: the workspace of the key ranges is missing or too small");
         GI_REQUIRE(rt.head_blocks * rt.splits <= 65535 && a.Hkv * rt.head_blocks <= 65535 && rt.splits <= 16,
                    "attention_rows: too many blocks of heads or ranges of keys (at most 16 ranges)");
-        const size_t smem_mma = rows_mma_smem(group, hd, vd, a.alias != 0);
-        if (own) return vd <= 64 ? launch_rows_mma<8, true>(a, rt, tiles, smem_mma, st) : launch_rows_mma<16, true>(a, rt, tiles, smem_mma, st);
-        if (vd <= 128) return launch_rows_mma<4, false>(a, rt, tiles, smem_mma, st);
-        if (vd <= 256) return launch_rows_mma<8, false>(a, rt, tiles, smem_mma, st);
-        return launch_rows_mma<16, false>(a, rt, tiles, smem_mma, st);
+        const size_t smem_mma = rows_mma_smem_of(mode, hd, vd, a.alias != 0);
+        if (mode == 1) return vd <= 64 ? launch_rows_mma<8, 1>(a, rt, tiles, smem_mma, st) : launch_rows_mma<16, 1>(a, rt, tiles, smem_mma, st);
+        if (mode == 2) return vd <= 256 ? launch_rows_mma<16, 2>(a, rt, tiles, smem_mma, st) : launch_rows_mma<32, 2>(a, rt, tiles, smem_mma, st);
+        if (vd <= 128) return launch_rows_mma<4, 0>(a, rt, tiles, smem_mma, st);
+        if (vd <= 256) return launch_rows_mma<8, 0>(a, rt, tiles, smem_mma, st);
+        return launch_rows_mma<16, 0>(a, rt, tiles, smem_mma, st);
     }
     // rows of the key tile: pairs of values are read by 32 lanes from 32 rows, free of bank conflicts when the row
     // length counted in pairs is odd

@@ -313,7 +313,8 @@ def attention_rows_tensor_cores(on: Optional[bool] = None) -> bool:
 def attention_rows_tile_tokens(num_heads: int, num_kv_heads: int, head_dim: int, value_dim: int, values_in_keys: bool) -> int:
     """How many consecutive tokens of one request share a tile of the tensor-core form of ``attention_rows`` over a
     bfloat16 cache (64 // heads per key/value head for head and value sizes up to 128, where every warp owns sixteen
-    rows; else 16 // heads per key/value head, at least 1); 0 when that form does not serve these sizes."""
+    rows; 2 for larger heads with sixteen or more heads per key/value head; else 16 // heads per key/value head, at
+    least 1); 0 when that form does not serve these sizes."""
     return int(lib().gi_attention_rows_tile_tokens(num_heads, num_kv_heads, head_dim, value_dim, int(values_in_keys)))
 
 

@@ -43,6 +43,7 @@ _SIGNATURES = {
     "gi_attention_rows_tile_tokens": [c_int, c_int, c_int, c_int, c_int],
     "gi_attention_rows_supported": [c_int, c_int],
     "gi_attention_rows_set_mma": [c_int],
+    "gi_attention_rows_set_pairs": [c_int],
     "gi_head_product": [c_void_p, c_int, c_longlong, c_int, c_int, c_void_p, c_int, c_longlong, c_void_p, c_int, c_longlong,
                         c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_float, c_void_p, c_void_p],
     "gi_expert_product": [c_void_p, c_int, c_longlong, c_int, c_void_p, c_int, c_longlong, c_int, c_longlong, c_int, c_int,

@@ -144,7 +144,8 @@ def test_attention_rows(dtype, H, Hkv, hd, vd, window, chunk, biased, sunk, alia
     (16, 1, 80, 64, 29, None, False, True, True),       # four tokens of sixteen heads over a latent of 64 + 16
     (8, 8, 32, 64, 20, None, False, False, False),      # 64 tokens to a tile
     (6, 2, 48, 128, 17, 25, True, True, False),         # groups of three: 21 tokens to a tile and a row left over
-    (40, 1, 144, 128, 64, None, False, True, True),     # the warps share sixteen rows: three blocks of heads, the last one half full
+    (40, 1, 144, 128, 64, None, False, True, True),     # two tokens of sixteen heads a block: three blocks of heads, the last one half full
+    (16, 1, 544, 512, 100, None, False, True, True),    # the same with the widest value
     (16, 2, 160, 192, 33, None, True, True, False),     # shared rows, two tokens of eight heads to a tile
 ])
 def test_attention_rows_in_tiles_and_ranges_of_keys(H, Hkv, hd, vd, window, chunk, biased, sunk, alias):
@@ -174,7 +175,7 @@ def test_attention_rows_in_tiles_and_ranges_of_keys(H, Hkv, hd, vd, window, chun
     p = pg.softmax_rows(scores, mask, None if sinks is None else sinks.double())
     want = torch.einsum("hij,jhd->ihd", p, v.double().repeat_interleave(per, 1)).reshape(n, H * vd)
     per_tile = kernels.attention_rows_tile_tokens(H, Hkv, hd, vd, alias)
-    assert per_tile == (64 // per if hd <= 128 and vd <= 128 and per <= 16 else max(1, 16 // per))
+    assert per_tile == (64 // per if hd <= 128 and vd <= 128 and per <= 16 else 2 if per >= 16 else max(1, 16 // per))
     # the step: rows 0..n-1 of one request in order; tiles start at an odd row so that they straddle blocks and pages
     tiles = [(0, 3, 0)] + [(t, min(per_tile, n - t), 0) for t in range(3, n, per_tile)] if per_tile >= 3 else \
         [(t, min(per_tile, n - t), 0) for t in range(0, n, per_tile)]
