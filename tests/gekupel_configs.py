@@ -65,6 +65,21 @@ GEK_B = {
 }
 
 
+# C: sizes that fit no tile: a width and ranks that are no multiples of 8, three heads, rotated parts of 12 and 6, value
+# sizes of 28 and 10, seven experts of 44 of which a token uses three, a window of 5 and blocks of 3 (shorter than a page),
+# a window of one token, and a layer that runs the weights of a later layer
+GEK_C = {
+    "architecture": "Gekupel", "embedding": {"scale": 2.5}, "norm": {"eps": 1e-4}, "vocab": 131, "width": 100,
+    "layers": [
+        attention(3, 3, 20, 28, 3, 0.35, mlp=moe(44, 7, 3), weights_of=2),
+        latent(3, 20, 12, 28, 36, 52, 5, 0.22, 77.0, scaling=(3.0, 8, 2.0, 0.25), mlp=moe(44, 7, 3)),
+        attention(3, 3, 20, 28, 3, 0.35, mlp=moe(44, 7, 3)),
+        latent(6, 10, 6, 10, 30, 34, 1, 0.5, 1000.0, mlp=dense(60)),
+        latent(3, 20, 12, 28, 36, 52, 5, 0.22, 77.0, scaling=(3.0, 8, 2.0, 0.25), mlp=moe(44, 7, 3), weights_of=1),
+    ],
+}
+
+
 def make_model_dir(config, seed, out_dir, dtype="bfloat16", std=0.12):
     from geneinfer_b200.weights import write_random_model
     return write_random_model(config, seed, out_dir, dtype, std=std)

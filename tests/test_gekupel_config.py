@@ -12,7 +12,7 @@ from geneinfer_b200.weights import load_model_folder
 
 
 def test_config_round_trip_and_translation():
-    for raw in (gc.GEK_A, gc.GEK_B):
+    for raw in (gc.GEK_A, gc.GEK_B, gc.GEK_C):
         arch, cfg = parse_config(raw)
         assert arch.name == "Gekupel" and cfg.to_json() == raw
         spec = cfg.model_spec()

@@ -577,13 +577,13 @@ def test_routed_experts_on_the_tensor_cores(T, E, top, D, I):
 
 # ------------------------------------------------------------------------------------------ whole models
 _TMP = {}
-LENGTHS = {"a": [1, 2, 3, 75, 20, 120, 47, 30], "b": [150, 4, 64, 1, 99]}
-CONFIGS = {"a": gc.GEK_A, "b": gc.GEK_B}
+LENGTHS = {"a": [1, 2, 3, 75, 20, 120, 47, 30], "b": [150, 4, 64, 1, 99], "c": [90, 2, 33, 1, 140, 17]}
+CONFIGS = {"a": gc.GEK_A, "b": gc.GEK_B, "c": gc.GEK_C}
 
 
 def _model_dir(case, tmp_path_factory):
     if case not in _TMP:
-        _TMP[case] = gc.make_model_dir(CONFIGS[case], 23 if case == "a" else 31, str(tmp_path_factory.mktemp("gekupel_" + case)))
+        _TMP[case] = gc.make_model_dir(CONFIGS[case], {"a": 23, "b": 31, "c": 37}[case], str(tmp_path_factory.mktemp("gekupel_" + case)))
     return _TMP[case]
 
 
@@ -622,7 +622,7 @@ def _engine(folder, dtype, n_pages, max_requests=4, page_size=16, max_step_token
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("case", ["a", "b"])
+@pytest.mark.parametrize("case", ["a", "b", "c"])
 def test_whole_prompts_decoding_portions_and_mixed_batches_agree_with_the_plain_model(case, dtype, tmp_path_factory):
     folder = _model_dir(case, tmp_path_factory)
     reqs, plain, tol = _requests(case), _plain(case, folder), _tolerance(case, folder, dtype)
