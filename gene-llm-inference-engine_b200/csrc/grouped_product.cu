@@ -15,9 +15,12 @@
 //   gather_rows       a[r] = x[sorted_rows[r] / top] (zeros for padding): the rows in the tiles' order
 //   route_combine     y[t] += sum_k weight[t, k] * part[row of pair t * top + k] in the order of k
 //
-// Products run on the CUDA cores with 32-bit fused multiply-adds in the order of k: the true 32-bit path, products of
-// few rows (decoding, where the expert weights stream once), and the bfloat16 path's fallback. An output element is
-// one chain of multiply-adds over its own row, whichever tile the row landed in.
+// Products run on the CUDA cores with 32-bit fused multiply-adds: the true 32-bit path, products of few rows (decoding,
+// where the weights stream once), the heads' matrices, and the bfloat16 path's fallback. Three forms: tiles of 16 x 64
+// outputs, tiles of 64 x 64 (many rows through the heads' matrices) and the few-row form further down. In the tiled forms
+// an output element is one chain of multiply-adds in the order of k over its own row, whichever tile the row landed in;
+// in the few-row form it is the sum of a warp's lanes' chains by a fixed tree. (Many rows through the experts' matrices
+// in bfloat16 run on the tensor cores: gi_gemm_tc_grouped.)
 #include "common.cuh"
 
 namespace gi {
@@ -466,12 +469,11 @@ route_combine_kernel(const float* __restrict__ part, const float* __restrict__ w
 // Whether every 16-byte load of the few-row form is aligned: pieces of the weights' rows and of the inputs' rows.
 static bool rows_form_fits(const GroupedArgs& p, int a_dtype, int w_dtype) {
     const int piece = w_dtype == kBF16 ? 8 : 4;
-    const size_t a_size = a_dtype == kBF16 ? 2 : 4, w_size = w_dtype == kBF16 ? 2 : 4;
+    const size_t a_size = a_dtype == kBF16 ? 2 : 4;
     if (a_dtype == kBF16 && w_dtype == kF32) return false;
     if (p.K % piece || p.ldw % piece || p.w_gs % piece || p.up_off % piece) return false;
     if (reinterpret_cast<uintptr_t>(p.w) % 16 || reinterpret_cast<uintptr_t>(p.a) % 16) return false;
     const int a_piece = static_cast<int>(16 / a_size);
-    (void)w_size;
     return p.lda % a_piece == 0 && p.a_off % a_piece == 0 && p.a_gs % a_piece == 0;
 }
 
